@@ -2,7 +2,8 @@
 
 One pool tensor per group of key/value layers, laid out
 ``[cache key, k|v, page, kv head, slot in page, head_dim]`` so that the keys of
-one (page, head) are one contiguous tile, and one ``[max_slots, max_pages]``
+one (page, head) are one contiguous tile (a group whose value heads have another
+size than its key heads has one such tensor for the keys and one for the values), and one ``[max_slots, max_pages]``
 int32 block table per group, which follows the host manager's tables write by write.
 Pages are not cleared when they are given back
 (src/tokamak/memory/paged_cache.py:51-52 clears only at start): a position is
@@ -89,12 +90,23 @@ class DeviceCache:
         self.slot_records = torch.zeros((manager.max_slots, SLOT_WORDS), dtype=torch.int32, device=device)
         self.slot_records[:, REC_LAST_TOKEN] = -1
         self._record_writes: dict[int, tuple[int, list[int]]] = {}
+        self._pool_groups: list[KVGroup] = []      # the group of every entry of _pools
         for gi, g in enumerate(manager.kv_groups):
-            pool = torch.zeros((len(g.cache_keys), 2, g.num_pages, g.need.n_kv_heads, g.page_size,
-                                g.need.head_dim), dtype=dtype, device=device)
-            self._pools.append(pool)
+            shape = (len(g.cache_keys), 2, g.num_pages, g.need.n_kv_heads, g.page_size)
+            if g.need.value_dim == g.need.head_dim:
+                pool = torch.zeros(shape + (g.need.head_dim,), dtype=dtype, device=device)
+                k_of, v_of = (lambda i, pool=pool: pool[i, 0]), (lambda i, pool=pool: pool[i, 1])
+                pools = [pool]
+            else:
+                k_pool = torch.zeros((shape[0], 1) + shape[2:] + (g.need.head_dim,), dtype=dtype, device=device)
+                v_pool = torch.zeros((shape[0], 1) + shape[2:] + (g.need.value_dim,), dtype=dtype, device=device)
+                k_of, v_of = (lambda i, t=k_pool: t[i, 0]), (lambda i, t=v_pool: t[i, 0])
+                pools = [k_pool, v_pool]
+            for pool in pools:
+                self._pools.append(pool)
+                self._pool_groups.append(g)
             for i, key in enumerate(g.cache_keys):
-                self._views[key] = KVView(pool[i, 0], pool[i, 1], self.tables[gi], g.page_size, g.need.window)
+                self._views[key] = KVView(k_of(i), v_of(i), self.tables[gi], g.page_size, g.need.window)
         for g in manager.state_groups:
             records = torch.zeros((len(g.cache_keys), manager.max_slots, *g.need.shape),
                                   dtype=_STATE_DTYPES[g.need.dtype], device=device)
@@ -111,8 +123,9 @@ class DeviceCache:
     def bytes_per_token(self) -> int:
         """Bytes of keys and values that one position occupies over all layers."""
         total = 0
-        for g, pool in zip(self.manager.kv_groups, self._pools):
-            total += len(g.cache_keys) * 2 * g.need.n_kv_heads * g.need.head_dim * pool.element_size()
+        elem = torch.empty((), dtype=self.dtype).element_size()
+        for g in self.manager.kv_groups:
+            total += len(g.cache_keys) * g.need.n_kv_heads * (g.need.head_dim + g.need.value_dim) * elem
         return total
 
     # ---- the engine's records ----------------------------------------------------------------
@@ -184,7 +197,7 @@ class DeviceCache:
 
     def poison_free_pages(self, value: float = float("nan")) -> None:
         """Overwrite every page that no request holds (a test aid: stale reads then show)."""
-        for g, pool in zip(self.manager.kv_groups, self._pools):
+        for g, pool in zip(self._pool_groups, self._pools):
             free = list(g.allocator._free)
             if free:
                 pool[:, :, torch.tensor(free, device=self.device)] = value

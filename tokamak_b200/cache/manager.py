@@ -45,13 +45,19 @@ class KVPagesNeed:
     """Cache need of a mixer that stores keys and values per position.
 
     ``window`` is the number of most recent positions a query sees (itself
-    included), or ``None`` when it sees all of them.
+    included), or ``None`` when it sees all of them.  ``v_head_dim`` is the size of a value
+    head where it differs from the key head's (``None``: the same).
     """
 
     n_kv_heads: int
     head_dim: int
     window: int | None = None
+    v_head_dim: int | None = None
     kind: str = "kv_pages"
+
+    @property
+    def value_dim(self) -> int:
+        return self.head_dim if self.v_head_dim is None else self.v_head_dim
 
 
 @dataclass(frozen=True)

@@ -1,7 +1,8 @@
 """The one registry from an architecture's name to its model.
 
 An architecture is two functions: ``parse_config`` turns the raw ``config.json``
-dictionary into a typed configuration, and ``model_spec`` turns that into the
+dictionary (and, for a design that leaves a size to the checkpoint, the tensors' shapes) into
+a typed configuration, and ``model_spec`` turns that into the
 parts, blocks and schedule of the model.  Adding an architecture is adding an
 entry (src/tokamak/config.py:20-26 is the reference's whitelist).
 
@@ -61,10 +62,17 @@ class Architecture:
     parse_config: Callable[..., Any]
     model_spec: Callable[..., Any]
     options: frozenset = frozenset()
+    reads_tensor_shapes: bool = False      # parse_config also takes tensor_shapes={name: shape}
 
-    def parse(self, raw: Mapping[str, Any], eos_token_ids=None) -> Any:
-        """The typed configuration, checked against the engine's protocol."""
-        return check_config_protocol(self.parse_config(raw, eos_token_ids), self.name)
+    def parse(self, raw: Mapping[str, Any], eos_token_ids=None, tensor_shapes=None) -> Any:
+        """The typed configuration, checked against the engine's protocol.  An architecture some of
+        whose sizes stand only in the checkpoint (``reads_tensor_shapes``) is also given the
+        names and shapes of the checkpoint's tensors, where the caller has them."""
+        if self.reads_tensor_shapes:
+            cfg = self.parse_config(raw, eos_token_ids, tensor_shapes=tensor_shapes)
+        else:
+            cfg = self.parse_config(raw, eos_token_ids)
+        return check_config_protocol(cfg, self.name)
 
     def build_spec(self, cfg: Any, **options: Any) -> Any:
         """The model as data, with the engine-wide options that were asked for (``None`` = not asked)."""
@@ -102,11 +110,20 @@ def supported_architectures() -> list[str]:
     return sorted(_ARCHITECTURES)
 
 
-def architecture_of(raw_config: Mapping[str, Any]) -> Architecture:
-    """The architecture named by ``architectures[0]`` of a config.json dictionary."""
-    _load_builtin()
+def architecture_name(raw_config: Mapping[str, Any]) -> str:
+    """The name a config.json dictionary gives its design: ``architectures[0]``, or the string
+    under ``architecture``."""
     names = raw_config.get("architectures") or []
-    name = names[0] if names else "<missing>"
+    if names:
+        return names[0]
+    name = raw_config.get("architecture")
+    return name if isinstance(name, str) and name else "<missing>"
+
+
+def architecture_of(raw_config: Mapping[str, Any]) -> Architecture:
+    """The architecture that a config.json dictionary names (see :func:`architecture_name`)."""
+    _load_builtin()
+    name = architecture_name(raw_config)
     if name not in _ARCHITECTURES:
         supported = ", ".join(sorted(_ARCHITECTURES))
         raise ConfigError(f"Unsupported architecture {name!r}; supported: {supported}")
@@ -118,3 +135,7 @@ def _load_builtin() -> None:
         from ..models import qwen3
         register_architecture(Architecture(qwen3.ARCHITECTURE, qwen3.parse_config, qwen3.model_spec,
                                            options=frozenset({"window"})))
+    if "Ketalix" not in _ARCHITECTURES:
+        from ..models import ketalix
+        register_architecture(Architecture(ketalix.ARCHITECTURE, ketalix.parse_config, ketalix.model_spec,
+                                           reads_tensor_shapes=True))

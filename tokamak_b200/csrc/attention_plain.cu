@@ -9,6 +9,11 @@
 // softmax_scale, the softmax is an online one with float32 running maximum,
 // normaliser and accumulator (paged_attention.py:111-123,139-151).  This is the
 // kernel of the float32 path and of every shape the tiled kernels refuse.
+//
+// Options that other designs use: values of another size than keys (v_dim), a soft cap on the
+// scaled scores (score <- cap * tanh(score / cap), cap <= 0: none), and a sink per query head:
+// a learned number whose exponential joins the softmax denominator once, with no key and no
+// value, neither scaled nor capped.
 #include "common.cuh"
 
 namespace tk {
@@ -18,9 +23,10 @@ constexpr int kPlainWarps = 4;
 
 struct AttnParams {
   const void* q;            // [n_tokens, n_q_heads, head_dim]
-  void* out;                // [n_tokens, n_q_heads, head_dim]
+  void* out;                // [n_tokens, n_q_heads, v_dim]
   const void* k_cache;      // [num_pages, n_kv_heads, page_size, head_dim]
-  const void* v_cache;
+  const void* v_cache;      // [num_pages, n_kv_heads, page_size, v_dim]
+  const float* sinks;       // [n_q_heads] or null
   const int* positions;     // [n_tokens]
   const int* tok_req;       // [n_tokens]
   const int* req_slot;      // [n_reqs]
@@ -28,8 +34,8 @@ struct AttnParams {
   const int* items;         // [n_items] token indices to process, or null for all tokens
   int* err;
   int n_tokens, n_reqs, n_q_heads, n_kv_heads, head_dim;
-  int page_size, max_pages, num_pages, window;
-  float scale;
+  int page_size, max_pages, num_pages, window, v_dim;
+  float scale, softcap;
 };
 
 template <typename T>
@@ -45,6 +51,7 @@ __global__ void attention_plain_kernel(AttnParams p) {
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   const int d = p.head_dim;
+  const int dv = p.v_dim;
   const int group = p.n_q_heads / p.n_kv_heads;
   const int hkv = hq / group;
   const int pos = p.positions[t];
@@ -66,6 +73,9 @@ __global__ void attention_plain_kernel(AttnParams p) {
     acc[i] = 0.0f;
   }
   float m = -INFINITY, l = 0.0f;
+  // the sink is one more term of the denominator: the first warp starts from it
+  if (p.sinks != nullptr && warp == 0) { m = p.sinks[hq]; l = 1.0f; }
+  const float inv_cap = p.softcap > 0.0f ? 1.0f / p.softcap : 0.0f;
 
   for (int j = lo + warp; j <= pos; j += kPlainWarps) {
     const int pidx = j / p.page_size;
@@ -74,9 +84,9 @@ __global__ void attention_plain_kernel(AttnParams p) {
       if (lane == 0) set_error(p.err, kErrPage, t, pidx, page);
       break;
     }
-    const size_t off = (((size_t)page * p.n_kv_heads + hkv) * p.page_size + (j % p.page_size)) * d;
-    const T* krow = (const T*)p.k_cache + off;
-    const T* vrow = (const T*)p.v_cache + off;
+    const size_t row = ((size_t)page * p.n_kv_heads + hkv) * p.page_size + (j % p.page_size);
+    const T* krow = (const T*)p.k_cache + row * d;
+    const T* vrow = (const T*)p.v_cache + row * dv;
     float dot = 0.0f;
 #pragma unroll
     for (int i = 0; i < kPlainMaxPerLane; ++i) {
@@ -84,6 +94,7 @@ __global__ void attention_plain_kernel(AttnParams p) {
       if (e < d) dot += qreg[i] * to_f32<T>(krow[e]);
     }
     dot = warp_sum(dot);
+    if (p.softcap > 0.0f) dot = p.softcap * tanhf(dot * inv_cap);
     const float m_new = fmaxf(m, dot);
     const float corr = expf(m - m_new);   // m = -inf on the first key: exp(-inf) = 0
     const float pj = expf(dot - m_new);
@@ -91,7 +102,7 @@ __global__ void attention_plain_kernel(AttnParams p) {
 #pragma unroll
     for (int i = 0; i < kPlainMaxPerLane; ++i) {
       const int e = i * 32 + lane;
-      if (e < d) acc[i] = acc[i] * corr + pj * to_f32<T>(vrow[e]);
+      if (e < dv) acc[i] = acc[i] * corr + pj * to_f32<T>(vrow[e]);
     }
     m = m_new;
   }
@@ -113,11 +124,11 @@ __global__ void attention_plain_kernel(AttnParams p) {
       l_all += s_l[w] * f[w];
     }
     const float inv = 1.0f / l_all;   // the query always sees its own key, so l_all > 0
-    T* orow = (T*)p.out + ((size_t)t * p.n_q_heads + hq) * d;
+    T* orow = (T*)p.out + ((size_t)t * p.n_q_heads + hq) * dv;
 #pragma unroll
     for (int i = 0; i < kPlainMaxPerLane; ++i) {
       const int e = i * 32 + lane;
-      if (e < d) {
+      if (e < dv) {
         float o = 0.0f;
 #pragma unroll
         for (int w = 0; w < kPlainWarps; ++w) o += s_acc[w][e] * f[w];
@@ -134,9 +145,10 @@ TK_API int tk_attention_plain(const void* q, void* out, const void* k_cache, con
                               const int* block_table, const int* items, int* err, int n_tokens, int n_reqs,
                               int n_q_heads, int n_kv_heads, int head_dim, int page_size,
                               int max_pages, int num_pages, int window, float scale, int dtype,
-                              cudaStream_t stream) {
+                              int v_dim, float softcap, const float* sinks, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
-  if (head_dim < 1 || head_dim > tk::kPlainMaxPerLane * 32 || n_kv_heads < 1 ||
+  if (v_dim <= 0) v_dim = head_dim;
+  if (head_dim < 1 || head_dim > tk::kPlainMaxPerLane * 32 || v_dim > tk::kPlainMaxPerLane * 32 || n_kv_heads < 1 ||
       n_q_heads % n_kv_heads != 0 || n_q_heads > 65535) {
     return (int)cudaErrorInvalidValue;
   }
@@ -146,6 +158,7 @@ TK_API int tk_attention_plain(const void* q, void* out, const void* k_cache, con
   p.items = items; p.err = err; p.n_tokens = n_tokens; p.n_reqs = n_reqs; p.n_q_heads = n_q_heads;
   p.n_kv_heads = n_kv_heads; p.head_dim = head_dim; p.page_size = page_size;
   p.max_pages = max_pages; p.num_pages = num_pages; p.window = window; p.scale = scale;
+  p.v_dim = v_dim; p.softcap = softcap; p.sinks = sinks;
   dim3 grid(n_tokens, n_q_heads);
   cudaError_t e = cudaSuccess;
   TK_DISPATCH_DTYPE(dtype, T,

@@ -9,10 +9,10 @@
 
 namespace tk {
 
-// resid[t, :] = float(table[ids[t], :])                 (src/tokamak/model/transformer.py:140)
+// resid[t, :] = float(table[ids[t], :]) * scale                 (src/tokamak/model/transformer.py:140)
 template <typename T>
 __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __restrict__ ids,
-                                    float* __restrict__ resid, int hidden, int vocab, int* err) {
+                                    float* __restrict__ resid, int hidden, int vocab, float scale, int* err) {
   pdl_trigger();
   if (threadIdx.x == 0) tl_mark(4, 0);
   pdl_wait();
@@ -26,7 +26,7 @@ __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __re
     return;
   }
   const T* row = table + (size_t)id * hidden;
-  for (int h = threadIdx.x; h < hidden; h += blockDim.x) out[h] = to_f32<T>(row[h]);
+  for (int h = threadIdx.x; h < hidden; h += blockDim.x) out[h] = to_f32<T>(row[h]) * scale;
 }
 
 // x = resid[r] (+ delta[r]);  resid[r] = x (when written back);
@@ -162,12 +162,19 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const T* __res
   }
 }
 
-// out[t, j] = silu(gate[t, j]) * up[t, j]           (src/tokamak/model/layers.py:103)
+// Activations of the gated unit: 0 = silu, 1 = the tanh form of gelu,
+// 0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3))).
+__device__ __forceinline__ float glu_act(float g, int act) {
+  if (act == 1) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+  return g / (1.0f + expf(-g));
+}
+
+// out[t, j] = act(gate[t, j]) * up[t, j]           (act = silu: src/tokamak/model/layers.py:103)
 // A row of gu holds gate and up alternating in blocks: `block` gate values, then the `block` up
 // values of the same outputs (block = inter: all gate values, then all up values).
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, const float* __restrict__ parts, int n_parts,
-                              size_t part_stride, T* __restrict__ out, int inter, int block, size_t total) {
+                              size_t part_stride, T* __restrict__ out, int inter, int block, size_t total, int act) {
   pdl_trigger();
   pdl_wait();
   size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -187,15 +194,14 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, const float* __restrict_
         u += parts[s * part_stride + at + block];
       }
     }
-    const float s = g / (1.0f + expf(-g));
-    out[idx] = from_f32<T>(s * u);
+    out[idx] = from_f32<T>(glu_act(g, act) * u);
   }
 }
 
 // The same for an intermediate size and a block that are multiples of 8: 16-byte loads and stores.
 template <typename T>
 __global__ void swiglu_vec_kernel(const T* __restrict__ gu, const float* __restrict__ parts, int n_parts,
-                                  size_t part_stride, T* __restrict__ out, int inter, int block, size_t total8) {
+                                  size_t part_stride, T* __restrict__ out, int inter, int block, size_t total8, int act) {
   pdl_trigger();
   pdl_wait();
   size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -221,7 +227,7 @@ __global__ void swiglu_vec_kernel(const T* __restrict__ gu, const float* __restr
       }
     }
 #pragma unroll
-    for (int e = 0; e < 8; ++e) y[e] = g[e] / (1.0f + expf(-g[e])) * u[e];
+    for (int e = 0; e < 8; ++e) y[e] = glu_act(g[e], act) * u[e];
     Vec8<T>::store(out + t * inter + j, y);
   }
 }
@@ -231,13 +237,13 @@ __global__ void swiglu_vec_kernel(const T* __restrict__ gu, const float* __restr
 TK_TIMELINE_SETTER(elementwise)
 
 TK_API int tk_embed_gather(const void* table, int dtype, const int* ids, float* resid, int n_tokens,
-                           int hidden, int vocab, int* err, cudaStream_t stream) {
+                           int hidden, int vocab, float scale, int* err, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   const int threads = hidden >= 1024 ? 256 : 128;
   cudaError_t e = cudaSuccess;
   TK_DISPATCH_DTYPE(dtype, T,
                     e = tk::launch(tk::embed_gather_kernel<T>, dim3(n_tokens), dim3(threads), 0, stream,
-                                       (const T*)table, ids, resid, hidden, vocab, err));
+                                       (const T*)table, ids, resid, hidden, vocab, scale, err));
   return (int)e;
 }
 
@@ -274,7 +280,7 @@ TK_API int tk_add_rmsnorm(float* resid, const void* delta, const float* parts, i
 }
 
 TK_API int tk_swiglu(const void* gate_up, const float* parts, int n_parts, long long part_stride,
-                     void* out, int n_tokens, int inter, int block, int dtype, cudaStream_t stream) {
+                     void* out, int n_tokens, int inter, int block, int dtype, int act, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (block <= 0 || inter % block != 0) return (int)cudaErrorInvalidValue;
   const size_t total = (size_t)n_tokens * inter;
@@ -287,7 +293,7 @@ TK_API int tk_swiglu(const void* gate_up, const float* parts, int n_parts, long 
     TK_DISPATCH_DTYPE(dtype, T,
                       e = tk::launch(tk::swiglu_vec_kernel<T>, dim3((unsigned)vblocks), dim3(threads), 0, stream,
                                      (const T*)gate_up, parts, n_parts, (size_t)part_stride, (T*)out, inter,
-                                     block, total8));
+                                     block, total8, act));
     return (int)e;
   }
   size_t blocks = (total + threads - 1) / threads;
@@ -295,6 +301,6 @@ TK_API int tk_swiglu(const void* gate_up, const float* parts, int n_parts, long 
   TK_DISPATCH_DTYPE(dtype, T,
                     e = tk::launch(tk::swiglu_kernel<T>, dim3((unsigned)blocks), dim3(threads), 0, stream,
                                    (const T*)gate_up, parts, n_parts, (size_t)part_stride, (T*)out, inter,
-                                   block, total));
+                                   block, total, act));
   return (int)e;
 }

@@ -16,7 +16,7 @@ _P = c_void_p
 
 # name -> argument types (every function returns a cudaError_t as int unless noted)
 _SIGNATURES: dict[str, list] = {
-    "tk_embed_gather": [_P, c_int, _P, _P, c_int, c_int, c_int, _P, _P],
+    "tk_embed_gather": [_P, c_int, _P, _P, c_int, c_int, c_int, c_float, _P, _P],
     "tk_step_begin": [_P, c_int, c_int, _P, c_int, _P, c_longlong, _P, _P, _P, _P, _P, c_int, c_int, _P, _P],
     "tk_decode_begin": [_P, c_int, c_int, _P, c_int, _P, c_longlong, _P, c_int, c_int, _P, _P, _P, _P, _P],
     "tk_sample_slots": [_P, c_longlong, _P, _P, c_int, _P, c_int, c_int, _P, _P],
@@ -28,14 +28,23 @@ _SIGNATURES: dict[str, list] = {
     "tk_gemm_chain_max_phases": [],
     "tk_slot_words": [],
     "tk_add_rmsnorm": [_P, _P, _P, c_int, c_longlong, _P, _P, _P, c_int, c_int, c_float, c_int, _P],
-    "tk_swiglu": [_P, _P, c_int, c_longlong, _P, c_int, c_int, c_int, c_int, _P],
+    "tk_swiglu": [_P, _P, c_int, c_longlong, _P, c_int, c_int, c_int, c_int, c_int, _P],
     "tk_rope_kv": [_P, _P, c_int, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
                    c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                    c_float, c_int, _P],
     "tk_rope_table": [_P, _P, _P, c_int, c_int, _P],
     "tk_attention_plain": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
                            c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                           c_float, c_int, _P],
+                           c_float, c_int, c_int, c_float, _P, _P],
+    "tk_branch_norm_add": [_P, _P, _P, c_int, c_longlong, _P, _P, _P, _P, _P, c_int, c_int, c_float, c_float,
+                           c_int, _P],
+    "tk_qkv_pairs": [_P, _P, c_int, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
+                     c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                     c_float, c_int, _P],
+    "tk_gla_decay": [_P, _P, c_int, c_int, c_int, _P, _P, _P, c_int, c_int, c_int, c_float, c_int, _P],
+    "tk_gla_scan": [_P, _P, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P, _P, _P, _P,
+                    c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, _P],
+    "tk_gla_out": [_P, _P, _P, c_int, c_int, c_int, _P, _P, c_int, c_int, c_int, c_float, c_int, _P],
     "tk_attention_decode": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
                             c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                             c_float, _P],

@@ -72,15 +72,16 @@ def dtype_code(dtype: torch.dtype) -> int:
         raise KernelError(f"unsupported element type {dtype}; the kernels take float32 and bfloat16")
 
 
-def embed_gather(table: torch.Tensor, ids: torch.Tensor, resid: torch.Tensor, err: torch.Tensor) -> None:
-    """resid[t] = float32(table[ids[t]])."""
+def embed_gather(table: torch.Tensor, ids: torch.Tensor, resid: torch.Tensor, err: torch.Tensor,
+                 scale: float = 1.0) -> None:
+    """resid[t] = float32(table[ids[t]]) * scale."""
     _want(table, None, "table"); _want(ids, torch.int32, "ids"); _want(resid, torch.float32, "resid")
     n = ids.numel()
     vocab, hidden = table.shape
     if resid.shape[-1] != hidden or resid.numel() < n * hidden:
         raise KernelError("resid is too small for the tokens")
     _check(_lib().tk_embed_gather(table.data_ptr(), dtype_code(table.dtype), ids.data_ptr(),
-                                     resid.data_ptr(), n, hidden, vocab, err.data_ptr(), _stream()),
+                                     resid.data_ptr(), n, hidden, vocab, float(scale), err.data_ptr(), _stream()),
            "embed_gather")
 
 
@@ -235,8 +236,11 @@ def add_rmsnorm(resid: torch.Tensor, delta: torch.Tensor | None, weight: torch.T
                                     float(eps), dtype_code(out.dtype), _stream()), "add_rmsnorm")
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor, block: int = 0) -> None:
-    """out[t, j] = silu(gate[t, j]) * up[t, j]; a row of ``gate_up`` holds ``block`` gate values,
+GLU_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor, block: int = 0, activation: str = "silu") -> None:
+    """out[t, j] = act(gate[t, j]) * up[t, j] with act = silu or the tanh form of gelu; a row of ``gate_up`` holds ``block`` gate values,
     then the ``block`` up values of the same outputs, and so on (``block = 0``: all I gate values,
     then all up values).  ``gate_up`` may be float32 partial sums ``[parts, tokens, 2I]`` that the
     kernel adds up first."""
@@ -256,8 +260,11 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor, block: int = 0) -> None:
     block = block or two_i // 2
     if (two_i // 2) % block:
         raise KernelError("the gate/up block must divide the intermediate size")
+    if activation not in GLU_ACTIVATIONS:
+        raise KernelError(f"unknown activation {activation!r}; known: {', '.join(GLU_ACTIVATIONS)}")
     _check(_lib().tk_swiglu(_ptr(gate_up), _ptr(parts), n_parts, part_stride, out.data_ptr(), n,
-                               two_i // 2, block, dtype_code(out.dtype), _stream()), "swiglu")
+                               two_i // 2, block, dtype_code(out.dtype), GLU_ACTIVATIONS[activation], _stream()),
+           "swiglu")
 
 
 def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:
@@ -334,16 +341,27 @@ def rope_kv(qkv: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor | None
 def attention_plain(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                     positions: torch.Tensor, tok_req: torch.Tensor, req_slot: torch.Tensor,
                     block_table: torch.Tensor, err: torch.Tensor, *, scale: float,
-                    window: int | None = None, items: torch.Tensor | None = None) -> None:
-    """Paged attention of a mixed batch; q and out are [N, Hq, d].
+                    window: int | None = None, items: torch.Tensor | None = None,
+                    softcap: float | None = None, sinks: torch.Tensor | None = None) -> None:
+    """Paged attention of a mixed batch; q is [N, Hq, d], out [N, Hq, dv] with dv the size of a
+    value head (``v_cache`` is ``[pages, Hkv, page, dv]``).
 
-    ``items`` restricts the work to the listed token indices (rows of q and out)."""
+    ``items`` restricts the work to the listed token indices (rows of q and out).  ``softcap``
+    bounds the scaled scores (``cap * tanh(score / cap)``); ``sinks`` is one float32 per query
+    head whose exponential joins the softmax denominator."""
     _want(q, None, "q"); _want(out, q.dtype, "out")
     _want(k_cache, q.dtype, "k_cache"); _want(v_cache, q.dtype, "v_cache")
     n, hq, d = q.shape
     num_pages, hkv, page_size, dk = k_cache.shape
-    if dk != d or v_cache.shape != k_cache.shape or out.shape != q.shape:
+    dv = v_cache.shape[3]
+    if dk != d or v_cache.shape[:3] != k_cache.shape[:3] or out.shape != (n, hq, dv):
         raise KernelError("attention shape mismatch")
+    if dv > 256:
+        raise KernelError(f"value size {dv} is beyond the kernels' limit of 256")
+    if sinks is not None:
+        _want(sinks, torch.float32, "sinks")
+        if sinks.numel() != hq:
+            raise KernelError("one sink per query head is needed")
     if hq % hkv:
         raise KernelError(f"{hq} query heads are not a multiple of {hkv} key/value heads")
     if d > 256:
@@ -354,8 +372,164 @@ def attention_plain(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v
                                         err.data_ptr(), n if items is None else items.numel(),
                                         req_slot.numel(), hq, hkv, d, page_size,
                                         block_table.shape[1], num_pages, int(window or 0),
-                                        float(scale), dtype_code(q.dtype), _stream()),
+                                        float(scale), dtype_code(q.dtype), dv, float(softcap or 0.0),
+                                        _ptr(sinks), _stream()),
            "attention_plain")
+
+
+def _parts_of(x: torch.Tensor, like: torch.dtype, name: str):
+    """(tensor | None, partial sums | None, number of parts, tokens, row length) of a product's
+    result: a 2-D tensor in the activation type, or 3-D float32 partial sums."""
+    if x.dim() == 3:
+        _want(x, torch.float32, name + " partial sums")
+        return None, x, x.shape[0], x.shape[1], x.shape[2]
+    _want(x, like, name)
+    return x, None, 0, x.shape[0], x.shape[1]
+
+
+def branch_norm_add(resid: torch.Tensor, branch: torch.Tensor, post_weight: torch.Tensor | None,
+                    layer_scale: torch.Tensor | None, branch_eps: float, next_weight: torch.Tensor | None,
+                    out: torch.Tensor | None, next_eps: float = 0.0, rows: torch.Tensor | None = None) -> None:
+    """``x = resid + rmsnorm(branch) * post_weight * layer_scale`` (written back unless ``rows``
+    selects rows), then ``out = rmsnorm(x) * next_weight`` if ``out`` is given.  ``branch`` is in
+    the activation type or float32 partial sums ``[parts, tokens, hidden]``."""
+    _want(resid, torch.float32, "resid")
+    hidden = resid.shape[-1]
+    dtype = out.dtype if out is not None else (branch.dtype if branch.dim() == 2 else torch.float32)
+    b, parts, n_parts, n, width = _parts_of(branch, dtype, "branch")
+    if width != hidden or n != resid.shape[0]:
+        raise KernelError("branch and resid differ in shape")
+    for name, t in (("post_weight", post_weight), ("layer_scale", layer_scale), ("next_weight", next_weight)):
+        if t is not None:
+            _want(t, torch.float32, name)
+            if t.numel() != hidden:
+                raise KernelError(f"{name} does not match the width")
+    if rows is not None:
+        _want(rows, torch.int32, "rows")
+    n_rows = rows.numel() if rows is not None else n
+    if out is not None:
+        _want(out, None, "out")
+        if next_weight is None or out.numel() < n_rows * hidden:
+            raise KernelError("out needs the weight of the norm that follows and room for the rows")
+    _check(_lib().tk_branch_norm_add(resid.data_ptr(), _ptr(b), _ptr(parts), n_parts,
+                                        parts.stride(0) if parts is not None else 0, _ptr(post_weight),
+                                        _ptr(layer_scale), _ptr(next_weight), _ptr(out), _ptr(rows), n_rows, hidden,
+                                        float(branch_eps), float(next_eps), dtype_code(dtype), _stream()),
+           "branch_norm_add")
+
+
+def qkv_pairs(qkv: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+              positions: torch.Tensor, tok_req: torch.Tensor, req_slot: torch.Tensor, block_table: torch.Tensor,
+              table: torch.Tensor | None, err: torch.Tensor, *, n_q_heads: int, n_kv_heads: int, rotary_dim: int,
+              unit_norm_eps: float | None, v_first_in: torch.Tensor | None = None,
+              v_lambda: torch.Tensor | None = None, v_first_out: torch.Tensor | None = None,
+              req_q_len: torch.Tensor | None = None, req_kv_len: torch.Tensor | None = None) -> None:
+    """Rotation of neighbouring pairs, unit norm of the rotated heads, blend of the values with an
+    earlier layer's, and the page write, for key heads of size ``d`` and value heads of size ``dv``.
+
+    ``qkv`` rows hold ``Hq d | Hkv d | Hkv dv`` values (activation type, or float32 partial sums).
+    ``v_first_in`` / ``v_first_out`` are float32 ``[tokens, Hkv dv]``; ``v_lambda`` one float32."""
+    _want(q_out, None, "q_out")
+    x, parts, n_parts, n, row = _parts_of(qkv, q_out.dtype, "qkv")
+    _want(k_cache, q_out.dtype, "k_cache"); _want(v_cache, q_out.dtype, "v_cache")
+    num_pages, hkv, page_size, d = k_cache.shape
+    dv = v_cache.shape[3]
+    if hkv != n_kv_heads or v_cache.shape[:3] != k_cache.shape[:3] or q_out.shape != (n, n_q_heads, d):
+        raise KernelError("cache pages or q_out do not match the heads")
+    if row < (n_q_heads + n_kv_heads) * d + n_kv_heads * dv:
+        raise KernelError("qkv rows are too short for the heads")
+    for name, t in (("positions", positions), ("tok_req", tok_req), ("req_slot", req_slot),
+                    ("block_table", block_table)):
+        _want(t, torch.int32, name)
+    if table is not None:
+        _want(table, torch.float32, "table")
+        if table.shape != (n, rotary_dim // 2, 2):
+            raise KernelError(f"the rotation table must be [{n}, {rotary_dim // 2}, 2], got {tuple(table.shape)}")
+    elif rotary_dim:
+        raise KernelError("rotary_dim without a rotation table")
+    for name, t in (("v_first_in", v_first_in), ("v_first_out", v_first_out)):
+        if t is not None:
+            _want(t, torch.float32, name)
+            if t.shape != (n, n_kv_heads * dv):
+                raise KernelError(f"{name} must be [{n}, {n_kv_heads * dv}]")
+    if v_first_in is not None:
+        _want(v_lambda, torch.float32, "v_lambda")
+    _check(_lib().tk_qkv_pairs(_ptr(x), _ptr(parts), n_parts, q_out.data_ptr(), k_cache.data_ptr(),
+                                  v_cache.data_ptr(), positions.data_ptr(), tok_req.data_ptr(), req_slot.data_ptr(),
+                                  block_table.data_ptr(), _ptr(req_q_len), _ptr(req_kv_len), _ptr(table),
+                                  _ptr(v_first_in), _ptr(v_lambda), _ptr(v_first_out), err.data_ptr(), n,
+                                  req_slot.numel(), n_q_heads, n_kv_heads, d, dv, rotary_dim, row, page_size,
+                                  block_table.shape[1], num_pages, 0 if unit_norm_eps is None else 1,
+                                  float(unit_norm_eps or 0.0), dtype_code(q_out.dtype), _stream()), "qkv_pairs")
+
+
+def gla_decay(proj: torch.Tensor, a_off: int, w2: torch.Tensor, bias: torch.Tensor | None, tau: float) -> torch.Tensor:
+    """``log(sigmoid(a W2^T + bias)) / tau`` in float32 ``[tokens, channels]``, where ``a`` are the
+    ``rank`` columns of ``proj`` from ``a_off`` on (``proj``: activation type or partial sums)."""
+    _want(w2, None, "w2")
+    channels, rank = w2.shape
+    x, parts, n_parts, n, row = _parts_of(proj, w2.dtype, "proj")
+    if a_off < 0 or a_off + rank > row:
+        raise KernelError("the low-rank columns lie outside the row")
+    if bias is not None:
+        _want(bias, torch.float32, "bias")
+        if bias.numel() != channels:
+            raise KernelError("one bias per channel is needed")
+    out = torch.empty((n, channels), dtype=torch.float32, device=w2.device)
+    _check(_lib().tk_gla_decay(_ptr(x), _ptr(parts), n_parts, row, a_off, w2.data_ptr(), _ptr(bias), out.data_ptr(),
+                                  n, channels, rank, float(tau), dtype_code(w2.dtype), _stream()), "gla_decay")
+    return out
+
+
+def gla_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, log_alpha: torch.Tensor, state: torch.Tensor,
+             req_q_start: torch.Tensor, req_q_len: torch.Tensor, req_slot: torch.Tensor, err: torch.Tensor, *,
+             q_scale: float, dtype: torch.dtype) -> torch.Tensor:
+    """The recurrence ``S = diag(alpha) S + k v^T, o = S^T (q_scale q)`` over every request's tokens of
+    the step; ``state`` is float32 ``[slots, heads, key_dim, value_dim]`` and is advanced in place.
+    Returns ``o`` float32 ``[tokens, heads, value_dim]``."""
+    _want(state, torch.float32, "state"); _want(log_alpha, torch.float32, "log_alpha")
+    n_slots, heads, dk, dv = state.shape
+    x, parts, n_parts, n, row = _parts_of(proj, dtype, "proj")
+    if log_alpha.shape != (n, heads * dk):
+        raise KernelError("log_alpha must be [tokens, heads * key_dim]")
+    for off, size in ((q_off, heads * dk), (k_off, heads * dk), (v_off, heads * dv)):
+        if off < 0 or off + size > row:
+            raise KernelError("a column range lies outside the row")
+    if dk > 512:
+        raise KernelError(f"key size {dk} is beyond the kernel's limit of 512")
+    for name, t in (("req_q_start", req_q_start), ("req_q_len", req_q_len), ("req_slot", req_slot)):
+        _want(t, torch.int32, name)
+    n_reqs = req_slot.numel()
+    out = torch.empty((n, heads, dv), dtype=torch.float32, device=state.device)
+    _check(_lib().tk_gla_scan(_ptr(x), _ptr(parts), n_parts, row, q_off, k_off, v_off, log_alpha.data_ptr(),
+                                 state.data_ptr(), out.data_ptr(), req_q_start.data_ptr(), req_q_len.data_ptr(),
+                                 req_slot.data_ptr(), err.data_ptr(), n, n_reqs, n_slots, heads, dk, dv,
+                                 float(q_scale), dtype_code(dtype), _stream()), "gla_scan")
+    return out
+
+
+def gla_out(o: torch.Tensor, proj: torch.Tensor | None, g_off: int, weight: torch.Tensor | None, eps: float,
+            dtype: torch.dtype) -> torch.Tensor:
+    """``rmsnorm(o) * weight * silu(gate)`` per (token, head) in the activation type
+    ``[tokens, heads * value_dim]``; the gate is read from ``proj`` at column ``g_off`` (``proj=None``: no gate)."""
+    _want(o, torch.float32, "o")
+    n, heads, dv = o.shape
+    x = parts = None
+    n_parts, row = 0, 0
+    if proj is not None:
+        x, parts, n_parts, n2, row = _parts_of(proj, dtype, "proj")
+        if n2 != n or g_off < 0 or g_off + heads * dv > row:
+            raise KernelError("the gate columns lie outside the row")
+    else:
+        g_off = -1
+    if weight is not None:
+        _want(weight, torch.float32, "weight")
+        if weight.numel() != dv:
+            raise KernelError("the norm weight does not match the value size")
+    y = torch.empty((n, heads * dv), dtype=dtype, device=o.device)
+    _check(_lib().tk_gla_out(o.data_ptr(), _ptr(x), _ptr(parts), n_parts, row, g_off, _ptr(weight), y.data_ptr(),
+                                n, heads, dv, float(eps), dtype_code(dtype), _stream()), "gla_out")
+    return y
 
 
 def decode_splits(n_items: int, n_kv_heads: int, max_kv_len: int) -> int:

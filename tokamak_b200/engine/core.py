@@ -12,7 +12,7 @@ from ..cache.manager import CacheManager
 from ..config import architecture_of, read_config_json, read_eos_token_ids
 from ..models.decoder import DecoderModel
 from ..parts.base import Runtime
-from ..weights.loader import load_tensors
+from ..weights.loader import checkpoint_shapes, load_tensors
 from .step import StepFunction
 
 logger = logging.getLogger(__name__)
@@ -84,7 +84,11 @@ class EngineCore:
             eos = None
         self.raw_config = raw_config
         self.architecture = architecture_of(raw_config)
-        self.config = self.architecture.parse(raw_config, eos)
+        shapes = None
+        if self.architecture.reads_tensor_shapes:
+            shapes = ({k: tuple(v.shape) for k, v in tensors.items()} if tensors is not None
+                      else checkpoint_shapes(model))
+        self.config = self.architecture.parse(raw_config, eos, tensor_shapes=shapes)
         self.spec = self.architecture.build_spec(self.config, window=window)
         rt = Runtime(device=self.device, dtype=self.dtype)
         if tensors is None:
@@ -127,7 +131,7 @@ class EngineCore:
         if not 0.0 < utilization <= 1.0:
             raise ValueError(f"memory_utilization must be in (0, 1], got {utilization}")
         elem = 4 if self.dtype == torch.float32 else 2
-        per_token = sum(2 * need.n_kv_heads * need.head_dim * elem
+        per_token = sum(need.n_kv_heads * (need.head_dim + need.value_dim) * elem
                         for need in self.model.cache_needs().values() if isinstance(need, KVPagesNeed))
         smallest = -(-self.max_seq_len // page_size) * page_size
         if per_token == 0:
@@ -173,6 +177,6 @@ def random_core(raw_config: dict, *, seed: int = 0, std: float = 0.02, norm_std:
     expected = DecoderModel.expected_tensors(spec)
     tensors = random_tensors(expected, seed, std, norm_std, dt, device=dev)
     for name, req in expected.items():
-        if req.role == "vector" and name in tensors:
+        if req.role in ("vector", "bias", "fraction") and name in tensors:
             tensors[name] = tensors[name].float()
     return EngineCore("<random>", dtype=dt, device=dev, tensors=tensors, raw_config=raw_config, **kwargs)

@@ -133,6 +133,129 @@ class Attention:
                     req_q_len=step.req_q_len, req_kv_len=step.req_kv_len)
 
 
+@dataclass(frozen=True)
+class CappedAttentionSpec:
+    """Sizes and constants of an attention mixer with the options of :class:`CappedAttention`.
+
+    ``head_dim`` is the size of a query or key head, ``v_head_dim`` of a value head.
+    ``unit_norm_eps`` switches the weightless RMS norm of the rotated q and k heads on.
+    ``softcap`` of ``None``: scores are not capped.  ``sinks``: one learned number per query head
+    joins the softmax denominator.  ``value_mix`` is ``None``, ``"source"`` (this layer's raw
+    values are kept for later layers of the step under the key ``value_mix_key``) or ``"blend"``
+    (this layer's values are blended with the kept ones by its learned ``mix`` scalar).
+    The ``*_name`` fields are the tensors' names after the part's prefix.
+    """
+
+    hidden_size: int
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    v_head_dim: int
+    position: object
+    softmax_scale: float
+    unit_norm_eps: float | None = None
+    window: int | None = None
+    softcap: float | None = None
+    sinks: bool = False
+    value_mix: str | None = None
+    value_mix_key: str = "value_mix"
+    q_name: str = "q"
+    k_name: str = "k"
+    v_name: str = "v"
+    o_name: str = "o"
+    sink_name: str = "sink"
+    mix_name: str = "vmix"
+    kind: str = "attention_capped"
+
+
+@MIXERS.register("attention_capped")
+class CappedAttention:
+    """Grouped-query attention over paged keys and values with a set of options that several
+    designs share: value heads of their own size, rotation of neighbouring pairs over part of the
+    head, a unit RMS norm of q and k after the rotation, scores bounded by ``cap * tanh(s / cap)``,
+    a sliding window, a sink in the softmax denominator, and values blended with those of the
+    first blending layer (``v <- (1 - lambda) v + lambda v_first``; the blended values are what
+    the pages hold).  Query head ``h`` reads key/value head ``h // (Hq / Hkv)``.
+
+    The q, k and v matrices are stacked into one operand.  Rotation, norm, blend and page write
+    are one kernel (``csrc/qkv_pairs.cu``); scores, softmax and the weighted sum run in float32
+    inside the attention kernels.
+    """
+
+    def __init__(self, spec: CappedAttentionSpec, prefix: str, tensors: dict[str, torch.Tensor], rt: Runtime):
+        if spec.num_heads % spec.num_kv_heads:
+            raise ValueError(f"{spec.num_heads} query heads are not a multiple of "
+                             f"{spec.num_kv_heads} key/value heads")
+        if max(spec.head_dim, spec.v_head_dim) > 256 or spec.head_dim % 2 or spec.v_head_dim % 2:
+            raise ValueError(f"head sizes {spec.head_dim} / {spec.v_head_dim} are not taken by the attention "
+                             f"kernels: they need even sizes up to 256")
+        if spec.value_mix not in (None, "source", "blend"):
+            raise ValueError(f"value_mix must be None, 'source' or 'blend', got {spec.value_mix!r}")
+        self.spec = spec
+        self.rt = rt
+        self.w_qkv = torch.cat([tensors[prefix + spec.q_name], tensors[prefix + spec.k_name],
+                                tensors[prefix + spec.v_name]], dim=0).contiguous()
+        self.w_o = tensors[prefix + spec.o_name]
+        self.sinks = tensors[prefix + spec.sink_name].contiguous() if spec.sinks else None
+        self.mix = tensors[prefix + spec.mix_name].reshape(1).contiguous() if spec.value_mix == "blend" else None
+        self.position = POSITIONS.get(spec.position.kind)(spec.position, tensors, rt)
+        if getattr(self.position, "PAIRING", None) != "neighbours":
+            raise ValueError(f"position encoding {spec.position.kind!r} does not rotate neighbouring pairs")
+        self.prefill_heads = spec.num_heads
+
+    @staticmethod
+    def expected_tensors(spec: CappedAttentionSpec, prefix: str) -> dict[str, TensorReq]:
+        h, d, dv = spec.hidden_size, spec.head_dim, spec.v_head_dim
+        out = {
+            prefix + spec.q_name: TensorReq((spec.num_heads * d, h)),
+            prefix + spec.k_name: TensorReq((spec.num_kv_heads * d, h)),
+            prefix + spec.v_name: TensorReq((spec.num_kv_heads * dv, h)),
+            prefix + spec.o_name: TensorReq((h, spec.num_heads * dv)),
+        }
+        if spec.sinks:
+            out[prefix + spec.sink_name] = TensorReq((spec.num_heads,), role="bias")
+        if spec.value_mix is not None:
+            # the source layer's scalar is stored too; it is loaded and never read
+            out[prefix + spec.mix_name] = TensorReq((), role="fraction")
+        out.update(POSITIONS.get(spec.position.kind).expected_tensors(spec.position))
+        return out
+
+    def cache_need(self) -> KVPagesNeed:
+        s = self.spec
+        return KVPagesNeed(s.num_kv_heads, s.head_dim, s.window, None if s.v_head_dim == s.head_dim else s.v_head_dim)
+
+    def GRAPH_SAFE(self) -> bool:
+        return graph_safe(self.position)
+
+    def weight_bytes(self) -> int:
+        return tensor_bytes(self.w_qkv, self.w_o, self.sinks, self.mix)
+
+    def forward(self, h, step, cache_view):
+        spec = self.spec
+        n = h.shape[0]
+        qkv = linear(h, self.w_qkv, err=step.err)
+        q = torch.empty((n, spec.num_heads, spec.head_dim), dtype=h.dtype, device=h.device)
+        table, rotary_dim = self.position.rotary_table(step)
+        v_in = v_out = None
+        key = ("value_mix", spec.value_mix_key)
+        if spec.value_mix == "source":
+            v_out = torch.empty((n, spec.num_kv_heads * spec.v_head_dim), dtype=torch.float32, device=h.device)
+            step.scratch[key] = v_out
+        elif spec.value_mix == "blend":
+            v_in = step.scratch.get(key)
+            if v_in is None or v_in.shape != (n, spec.num_kv_heads * spec.v_head_dim):
+                raise RuntimeError("a blending attention layer ran before the layer whose values it blends with, "
+                                   "or their value heads differ in number or size")
+        ops.qkv_pairs(qkv, q, cache_view.k, cache_view.v, step.positions, step.tok_req, step.req_slot,
+                      cache_view.table, table, step.err, n_q_heads=spec.num_heads, n_kv_heads=spec.num_kv_heads,
+                      rotary_dim=rotary_dim, unit_norm_eps=spec.unit_norm_eps, v_first_in=v_in, v_lambda=self.mix,
+                      v_first_out=v_out, req_q_len=step.req_q_len, req_kv_len=step.req_kv_len)
+        out = torch.empty((n, spec.num_heads, spec.v_head_dim), dtype=h.dtype, device=h.device)
+        paged_attention(q, out, cache_view, step, scale=spec.softmax_scale, window=spec.window,
+                        softcap=spec.softcap, sinks=self.sinks)
+        return linear(out.view(n, spec.num_heads * spec.v_head_dim), self.w_o, err=step.err)
+
+
 _SIDE: dict = {}
 
 
@@ -146,8 +269,12 @@ def _side_stream(device: torch.device):
 
 
 def paged_attention(q: torch.Tensor, out: torch.Tensor, cache_view, step, *, scale: float,
-                    window: int | None) -> None:
+                    window: int | None, softcap: float | None = None, sinks: torch.Tensor | None = None) -> None:
     """Attention of every token of the step over the pages of its own request.
+
+    ``softcap`` bounds the scaled scores by ``cap * tanh(score / cap)``; ``sinks`` (float32, one per
+    query head) adds ``exp(sink)`` to every softmax denominator.  ``out`` is ``[N, Hq, dv]`` where
+    the value heads have a size of their own.
 
     Chooses the kernels.  bfloat16 with a head_dim the tiled kernels take: single next
     tokens go to the split-K decode kernel, portions of prompts to the tcgen05 flash
@@ -160,8 +287,10 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, cache_view, step, *, sca
     bf16 = q.dtype == torch.bfloat16
     n_dec = step.decode_items.numel()
     n_pf = step.prefill_items.numel()
-    dec_tiled = bf16 and n_dec > 0 and ops.decode_kernel_takes(hq, hkv, d, page)
-    pf_tiled = bf16 and n_pf > 0 and ops.prefill_kernel_takes(hq, hkv, d, page)
+    # the tiled kernels take heads of one size for keys and values, and neither cap nor sinks
+    plain_only = cache_view.v.shape[3] != d or softcap is not None or sinks is not None
+    dec_tiled = bf16 and n_dec > 0 and not plain_only and ops.decode_kernel_takes(hq, hkv, d, page)
+    pf_tiled = bf16 and n_pf > 0 and not plain_only and ops.prefill_kernel_takes(hq, hkv, d, page)
     # In a mixed step the two kernels touch different tokens.  One portion against a long context
     # is few blocks (one per pair of 128-row query tiles and head), so the decode kernel runs
     # beside it on a second stream instead of after it.
@@ -198,4 +327,4 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, cache_view, step, *, sca
         items = None if (dec_rest and pf_rest) else (step.decode_items if dec_rest else step.prefill_items)
         ops.attention_plain(q, out, cache_view.k, cache_view.v, step.positions, step.tok_req,
                             step.req_slot, cache_view.table, step.err, scale=scale, window=window,
-                            items=items)
+                            items=items, softcap=softcap, sinks=sinks)

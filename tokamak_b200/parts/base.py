@@ -94,6 +94,8 @@ class TensorReq:
     ``role`` decides the element type in memory: ``matrix`` takes the engine's
     dtype; ``vector`` (norm weights and other small per-channel tensors) is held in
     float32, which keeps a tensor stored in 32-bit exact; ``int_table`` becomes int32.
+    ``bias`` and ``fraction`` are held like ``vector`` and differ only in what seeded random
+    weights put there: values around 0, or inside (0, 1), instead of around 1.
     """
 
     shape: tuple[int, ...]
@@ -173,6 +175,24 @@ def tensor_bytes(*tensors: Any) -> int:
 
 
 SWAPPED_GEMM_MAX_TOKENS = 64
+
+
+@dataclass
+class NormedBranch:
+    """A branch output that joins the residual stream only after a norm of its own:
+    ``resid += rmsnorm(x, eps) * weight * layer_scale``.
+
+    A block whose sublayers are normalised on the way out leaves this as its pending value; the
+    norm that consumes it (:meth:`RMSNorm.add_norm <tokamak_b200.parts.norm.RMSNorm.add_norm>`)
+    does the output norm, the layer scale, the residual sum and its own normalisation in one
+    kernel.  ``x`` is what :func:`linear` returned (activation type, or float32 partial sums);
+    ``weight`` and ``layer_scale`` are float32 vectors or ``None``.
+    """
+
+    x: torch.Tensor
+    weight: torch.Tensor | None
+    eps: float
+    layer_scale: torch.Tensor | None = None
 
 
 @dataclass

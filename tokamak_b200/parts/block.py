@@ -6,7 +6,8 @@ from dataclasses import dataclass
 
 import torch
 
-from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, OwedNorm, Runtime, TensorReq, graph_safe, weight_bytes
+from .base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, NormedBranch, OwedNorm, Runtime, TensorReq, graph_safe,
+                   weight_bytes)
 
 
 @dataclass(frozen=True)
@@ -97,3 +98,109 @@ class PreNormBlock:
         h = self.norm2.add_norm(resid, a)
         out = self._branch(self.feed_forward, h, (step,), (resid, next_norm) if next_norm is not None else None)
         return resid, out
+
+
+@dataclass(frozen=True)
+class SandwichBlockSpec:
+    """A block whose sublayers are normalised on the way in and on the way out, with a learned
+    per-channel scale on what joins the residual stream.  ``feed_forward`` of ``None`` is a
+    block of one sublayer.  The ``*_name`` fields are full tensor names (``None``: no layer
+    scale); the prefixes end with a dot.
+    """
+
+    name: str
+    norm_in1: object
+    mixer: object
+    norm_out1: object
+    norm_in1_name: str
+    mixer_prefix: str
+    norm_out1_name: str
+    scale1_name: str | None = None
+    norm_in2: object = None
+    feed_forward: object = None
+    norm_out2: object = None
+    norm_in2_name: str | None = None
+    ffn_prefix: str | None = None
+    norm_out2_name: str | None = None
+    scale2_name: str | None = None
+    kind: str = "sandwich"
+
+
+@BLOCKS.register("sandwich")
+class SandwichBlock:
+    """``x = x + s1 * norm_out1(mixer(norm_in1(x)))``, then, if the block has a feed-forward,
+    ``x = x + s2 * norm_out2(ffn(norm_in2(x)))``, with ``s1`` and ``s2`` per-channel scales.
+
+    A sublayer's output is left as a :class:`NormedBranch`; the norm in front of the next
+    sublayer (this block's, the next block's, or the model's last norm) normalises it, scales
+    it, adds it to the float32 residual stream and normalises the sum, in one kernel.
+    """
+
+    def __init__(self, spec: SandwichBlockSpec, tensors: dict[str, torch.Tensor], rt: Runtime):
+        self.spec = spec
+        self.norm_in1 = NORMS.get(spec.norm_in1.kind)(spec.norm_in1, spec.norm_in1_name, tensors, rt)
+        self.mixer = MIXERS.get(spec.mixer.kind)(spec.mixer, spec.mixer_prefix, tensors, rt)
+        self.norm_out1 = NORMS.get(spec.norm_out1.kind)(spec.norm_out1, spec.norm_out1_name, tensors, rt)
+        self.scale1 = tensors[spec.scale1_name] if spec.scale1_name else None
+        self.feed_forward = self.norm_in2 = self.norm_out2 = self.scale2 = None
+        if spec.feed_forward is not None:
+            self.norm_in2 = NORMS.get(spec.norm_in2.kind)(spec.norm_in2, spec.norm_in2_name, tensors, rt)
+            self.feed_forward = FEED_FORWARDS.get(spec.feed_forward.kind)(spec.feed_forward, spec.ffn_prefix, tensors, rt)
+            self.norm_out2 = NORMS.get(spec.norm_out2.kind)(spec.norm_out2, spec.norm_out2_name, tensors, rt)
+            self.scale2 = tensors[spec.scale2_name] if spec.scale2_name else None
+        for norm in (self.norm_out1, self.norm_out2):
+            if norm is not None and not hasattr(norm, "owed_norm_params"):
+                raise ValueError("the norm after a sublayer must hand out its weight and eps (owed_norm_params)")
+
+    @staticmethod
+    def expected_tensors(spec: SandwichBlockSpec) -> dict[str, TensorReq]:
+        out: dict[str, TensorReq] = {}
+        out.update(NORMS.get(spec.norm_in1.kind).expected_tensors(spec.norm_in1, spec.norm_in1_name))
+        out.update(MIXERS.get(spec.mixer.kind).expected_tensors(spec.mixer, spec.mixer_prefix))
+        out.update(NORMS.get(spec.norm_out1.kind).expected_tensors(spec.norm_out1, spec.norm_out1_name))
+        if spec.scale1_name:
+            out[spec.scale1_name] = TensorReq((spec.norm_out1.dim,), role="vector")
+        if spec.feed_forward is not None:
+            out.update(NORMS.get(spec.norm_in2.kind).expected_tensors(spec.norm_in2, spec.norm_in2_name))
+            out.update(FEED_FORWARDS.get(spec.feed_forward.kind).expected_tensors(spec.feed_forward, spec.ffn_prefix))
+            out.update(NORMS.get(spec.norm_out2.kind).expected_tensors(spec.norm_out2, spec.norm_out2_name))
+            if spec.scale2_name:
+                out[spec.scale2_name] = TensorReq((spec.norm_out2.dim,), role="vector")
+        return out
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def _parts(self) -> list:
+        return [p for p in (self.norm_in1, self.mixer, self.norm_out1, self.norm_in2, self.feed_forward,
+                            self.norm_out2) if p is not None]
+
+    def GRAPH_SAFE(self) -> bool:
+        return graph_safe(*self._parts())
+
+    @property
+    def prefill_heads(self) -> int | None:
+        return getattr(self.mixer, "prefill_heads", None)
+
+    def weight_bytes(self) -> int:
+        extra = sum(t.numel() * t.element_size() for t in (self.scale1, self.scale2) if t is not None)
+        return weight_bytes(*self._parts()) + extra
+
+    @property
+    def entry_norm(self):
+        return self.norm_in1
+
+    @staticmethod
+    def _leave(x, norm, scale) -> NormedBranch:
+        weight, eps = norm.owed_norm_params()
+        return NormedBranch(x, weight, eps, scale)
+
+    def forward(self, resid: torch.Tensor, pending, step, cache_view):
+        h = self.norm_in1.add_norm(resid, pending)
+        if isinstance(h, OwedNorm):
+            h = h.materialize()
+        pending = self._leave(self.mixer.forward(h, step, cache_view), self.norm_out1, self.scale1)
+        if self.feed_forward is not None:
+            h = self.norm_in2.add_norm(resid, pending)
+            pending = self._leave(self.feed_forward.forward(h, step), self.norm_out2, self.scale2)
+        return resid, pending

@@ -16,6 +16,7 @@ class EmbeddingSpec:
     hidden_size: int
     name: str = "model.embed_tokens.weight"
     kind: str = "embedding"
+    scale: float = 1.0          # the looked-up rows are multiplied by it (in float32)
 
 
 @dataclass(frozen=True)
@@ -32,8 +33,8 @@ class HeadSpec:
 
 @EMBEDDINGS.register("embedding")
 class Embedding:
-    """Row lookup without scaling (src/tokamak/model/transformer.py:140); the rows
-    are widened into the float32 residual stream."""
+    """Row lookup (src/tokamak/model/transformer.py:140), times the spec's ``scale`` where a
+    design has one; the rows are widened into the float32 residual stream."""
 
     GRAPH_SAFE = True
 
@@ -51,7 +52,7 @@ class Embedding:
     def forward(self, step) -> torch.Tensor:
         resid = torch.empty((step.n_tokens, self.spec.hidden_size), dtype=torch.float32,
                             device=self.weight.device)
-        ops.embed_gather(self.weight, step.token_ids, resid, step.err)
+        ops.embed_gather(self.weight, step.token_ids, resid, step.err, scale=self.spec.scale)
         return resid
 
 

@@ -13,9 +13,16 @@ from .base import (FEED_FORWARDS, SWAPPED_GEMM_MAX_TOKENS, OwedNorm, Runtime, Te
 
 @dataclass(frozen=True)
 class SwiGLUSpec:
+    """A gated unit ``down(act(gate(x)) * up(x))``; ``activation`` is ``silu`` (SwiGLU) or
+    ``gelu_tanh``; the three names are the tensors' names after the part's prefix."""
+
     hidden_size: int
     intermediate_size: int
     kind: str = "swiglu"
+    activation: str = "silu"
+    gate_name: str = "gate_proj.weight"
+    up_name: str = "up_proj.weight"
+    down_name: str = "down_proj.weight"
 
 
 @FEED_FORWARDS.register("swiglu")
@@ -28,12 +35,18 @@ class SwiGLU:
     128-row tile of the decode product then holds both halves of 64 outputs, and the block
     that adds its K splits up applies the activation itself, so that decoding needs no
     activation kernel and no float32 round trip of the ``[tokens, 2I]`` sums.
+
+    With another activation than silu (the tanh form of gelu) the products run unfused and
+    the activation kernel applies it.
     """
 
     def __init__(self, spec: SwiGLUSpec, prefix: str, tensors: dict[str, torch.Tensor], rt: Runtime):
         self.spec = spec
         self.rt = rt
-        gate, up = tensors[prefix + "gate_proj.weight"], tensors[prefix + "up_proj.weight"]
+        if spec.activation not in ops.GLU_ACTIVATIONS:
+            raise ValueError(f"unknown activation {spec.activation!r}; known: {', '.join(ops.GLU_ACTIVATIONS)}")
+        self.fused_act = spec.activation == "silu"      # the products' fused epilogues apply silu
+        gate, up = tensors[prefix + spec.gate_name], tensors[prefix + spec.up_name]
         i, h = spec.intermediate_size, spec.hidden_size
         b = ops.SWIGLU_TILE_BLOCK
         if i % b == 0:
@@ -43,15 +56,15 @@ class SwiGLU:
             self.block = i
             self.w_gate_up = torch.cat((gate, up), dim=0)
         self.w_gate_up = self.w_gate_up.contiguous()
-        self.w_down = tensors[prefix + "down_proj.weight"]
+        self.w_down = tensors[prefix + spec.down_name]
 
     @staticmethod
     def expected_tensors(spec: SwiGLUSpec, prefix: str) -> dict[str, TensorReq]:
         h, i = spec.hidden_size, spec.intermediate_size
         return {
-            prefix + "gate_proj.weight": TensorReq((i, h)),
-            prefix + "up_proj.weight": TensorReq((i, h)),
-            prefix + "down_proj.weight": TensorReq((h, i)),
+            prefix + spec.gate_name: TensorReq((i, h)),
+            prefix + spec.up_name: TensorReq((i, h)),
+            prefix + spec.down_name: TensorReq((h, i)),
         }
 
     GRAPH_SAFE = True
@@ -66,7 +79,7 @@ class SwiGLU:
         err = step.err if step is not None else None
         chain = chain_of(step)
         n = h.shape[0]
-        if (h.dtype == torch.bfloat16 and err is not None and n <= SWAPPED_GEMM_MAX_TOKENS
+        if (self.fused_act and h.dtype == torch.bfloat16 and err is not None and n <= SWAPPED_GEMM_MAX_TOKENS
                 and self.block == ops.SWIGLU_TILE_BLOCK and self.spec.hidden_size % 8 == 0):
             splits, stages, cluster = ops.swapped_gemm_plan(2 * self.spec.intermediate_size, self.spec.hidden_size, n)
             colscale = None
@@ -77,12 +90,12 @@ class SwiGLU:
         else:
             if isinstance(h, OwedNorm):
                 h = h.materialize()
-            if (h.dtype == torch.bfloat16 and err is not None and self.block == ops.SWIGLU_TILE_BLOCK
+            if (self.fused_act and h.dtype == torch.bfloat16 and err is not None and self.block == ops.SWIGLU_TILE_BLOCK
                     and ops.pair_gemm_takes(n, 2 * self.spec.intermediate_size, self.spec.hidden_size, fused=True)):
                 # many tokens: the product on pairs of SMs applies the activation to its accumulators
                 act = ops.gemm_pair(h, self.w_gate_up, err, swiglu=True)
             else:
                 gate_up = linear(h, self.w_gate_up, err=err)
                 act = torch.empty((n, self.spec.intermediate_size), dtype=h.dtype, device=h.device)
-                ops.swiglu(gate_up, act, block=self.block)
+                ops.swiglu(gate_up, act, block=self.block, activation=self.spec.activation)
         return linear(act, self.w_down, err=err, then_norm=then_norm, chain=chain)

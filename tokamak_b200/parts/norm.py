@@ -7,7 +7,7 @@ from dataclasses import dataclass
 import torch
 
 from ..csrc import ops
-from .base import NORMS, OwedNorm, Runtime, TensorReq
+from .base import NORMS, NormedBranch, OwedNorm, Runtime, TensorReq
 
 
 @dataclass(frozen=True)
@@ -52,7 +52,14 @@ class RMSNorm:
         normalised and ``resid`` is left as it is.  ``delta`` may be an
         :class:`OwedNorm`: the branch has been added to ``resid`` already; if it was
         prepared for this norm it is handed on as it is (its consumer pays the scale).
+        A :class:`NormedBranch` is normalised, scaled and added by the same kernel.
         """
+        if isinstance(delta, NormedBranch):
+            n = rows.numel() if rows is not None else resid.shape[0]
+            out = torch.empty((n, self.spec.dim), dtype=self.rt.dtype, device=resid.device)
+            ops.branch_norm_add(resid, delta.x, delta.weight, delta.layer_scale, delta.eps, self.weight, out,
+                                self.spec.eps, rows)
+            return out
         if isinstance(delta, OwedNorm):
             if delta.norm is self:
                 return delta if rows is None else delta.rows(rows)

@@ -59,6 +59,47 @@ class RopeNeox:
         return table, self.spec.head_dim
 
 
+@dataclass(frozen=True)
+class RopePairsSpec:
+    """Rotation of neighbouring pairs (elements 2i and 2i+1) over the first ``rotary_dim``
+    elements of a head; the rest passes unrotated."""
+
+    rotary_dim: int
+    theta: float
+    kind: str = "rope_pairs"
+
+
+@POSITIONS.register("rope_pairs")
+class RopePairs:
+    """Rotary embedding in the interleaved layout: pair ``i`` of a head, ``(x[2i], x[2i+1])``,
+    turns by ``position * theta ** (-2i / rotary_dim)``.  The frequencies are rounded to
+    float32 once; position times frequency, cosine and sine are float32, once per step."""
+
+    GRAPH_SAFE = True
+    PAIRING = "neighbours"       # the mixer hands the table to a kernel that rotates (2i, 2i+1)
+
+    def __init__(self, spec: RopePairsSpec, tensors: dict, rt: Runtime):
+        if spec.rotary_dim % 2 or spec.rotary_dim < 0:
+            raise ValueError(f"the rotated part of a head must be even, got {spec.rotary_dim}")
+        self.spec = spec
+        idx = torch.arange(0, spec.rotary_dim, 2, dtype=torch.float64)
+        self.inv_freq = (float(spec.theta) ** (-idx / max(spec.rotary_dim, 1))).to(torch.float32).to(rt.device)
+
+    @staticmethod
+    def expected_tensors(spec: RopePairsSpec) -> dict:
+        return {}
+
+    def rotary_table(self, step) -> tuple[torch.Tensor | None, int]:
+        if self.spec.rotary_dim == 0:
+            return None, 0
+        key = ("rope_table", self.spec)
+        table = step.scratch.get(key)
+        if table is None:
+            table = ops.rope_table(step.positions, self.inv_freq)
+            step.scratch[key] = table
+        return table, self.spec.rotary_dim
+
+
 @POSITIONS.register("none")
 class NoPosition:
     """No position encoding: queries and keys pass unrotated."""

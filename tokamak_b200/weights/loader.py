@@ -45,12 +45,24 @@ def checkpoint_files(model_dir: str | Path) -> list[Path]:
     return files
 
 
+def checkpoint_shapes(model_dir: str | Path) -> dict[str, tuple]:
+    """Name -> shape of every tensor of a folder, from the files' headers alone."""
+    from safetensors import safe_open
+
+    shapes: dict[str, tuple] = {}
+    for file in checkpoint_files(model_dir):
+        with safe_open(str(file), framework="pt", device="cpu") as f:
+            for name in f.keys():
+                shapes[name] = tuple(f.get_slice(name).get_shape())
+    return shapes
+
+
 def target_dtype(req: TensorReq, stored: torch.dtype, engine_dtype: torch.dtype) -> torch.dtype:
     """Element type in memory: matrices follow the engine, per-channel vectors are
     float32 (exact for bfloat16 and for 32-bit storage), integer tables are int32."""
     if req.role == "int_table" or not stored.is_floating_point:
         return torch.int32
-    if req.role == "vector":
+    if req.role in ("vector", "bias", "fraction"):
         return torch.float32
     return engine_dtype
 

@@ -1,7 +1,7 @@
 """Seeded random weights: a model folder from a configuration and a seed.
 
 Matrices and the embedding are drawn from N(0, std), norm weights from
-1 + N(0, norm_std), tensor after tensor in the order of the model's expected
+1 + N(0, norm_std) (biases from N(0, 0.5), fractions from U(0.2, 0.8)), tensor after tensor in the order of the model's expected
 names from one CPU generator, so that a (configuration, seed) pair names one
 model.  The folder holds ``config.json`` and ``model.safetensors`` under the
 checkpoint names, so anything that reads such folders can load it.
@@ -32,6 +32,10 @@ def random_tensors(expected: Mapping[str, TensorReq], seed: int, std: float = 0.
             continue
         if req.role == "vector":
             t = 1.0 + norm_std * torch.randn(req.shape, generator=gen, dtype=torch.float32, device=device)
+        elif req.role == "bias":
+            t = 0.5 * torch.randn(req.shape, generator=gen, dtype=torch.float32, device=device)
+        elif req.role == "fraction":
+            t = 0.2 + 0.6 * torch.rand(req.shape, generator=gen, dtype=torch.float32, device=device)
         elif req.role == "int_table":
             t = torch.zeros(req.shape, dtype=torch.int32, device=device)
         else:
