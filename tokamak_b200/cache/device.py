@@ -195,6 +195,16 @@ class DeviceCache:
                 "temperature": flt(w[REC_TEMPERATURE]), "top_k": w[REC_TOP_K], "top_p": flt(w[REC_TOP_P]),
                 "last_token": w[REC_LAST_TOKEN]}
 
+    def poison_free_state(self, value: float = float("nan")) -> None:
+        """Overwrite the mixer state records of every slot that no request holds (a test aid: a
+        record that is not cleared when its slot is handed out then shows)."""
+        free = list(self.manager._free_slots)
+        if free and self._states:
+            index = torch.tensor(free, dtype=torch.long, device=self.device)
+            for records in self._states:
+                if records.is_floating_point():
+                    records.index_fill_(1, index, value)
+
     def poison_free_pages(self, value: float = float("nan")) -> None:
         """Overwrite every page that no request holds (a test aid: stale reads then show)."""
         for g, pool in zip(self._pool_groups, self._pools):
