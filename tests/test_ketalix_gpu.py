@@ -245,6 +245,59 @@ def test_attention_cap_sink_window_edges_and_page_borders(dtype, d, dv, H, G, pa
         assert (out.cpu().double() - want).abs().max() > 0.05
 
 
+@pytest.mark.parametrize("d,H,G,page,window,cap", [(64, 4, 2, 16, 40, 12.0), (128, 8, 2, 16, 33, 20.0),
+                                                    (128, 4, 4, 32, None, None), (64, 8, 1, 64, 70, 9.0)])
+def test_tiled_attention_kernels_in_prompts_and_in_decoding(d, H, G, page, window, cap):
+    """The dispatcher's bfloat16 path (tensor-core kernels for portions and for single tokens) on a
+    batch laid out by the step function: a prompt in two portions, then tokens one by one, with
+    stand-out keys just inside and just outside the window of the queries that are checked, one of
+    them at a page's border, and large sinks."""
+    from tokamak_b200.cache.device import DeviceCache, plan_groups
+    from tokamak_b200.cache.manager import CacheManager, KVPagesNeed
+    from tokamak_b200.engine.step import StepEntry, StepFunction
+    from tokamak_b200.parts.attention import paged_attention
+    T, n_dec = 300, 40
+    g = torch.Generator().manual_seed(d + page)
+    q = torch.randn(T, H, d, generator=g)
+    k = torch.randn(T, G, d, generator=g)
+    v = torch.randn(T, G, d, generator=g)
+    w = window or T
+    for iq in list(range(T - n_dec - 2, T, 7)) + [4 * page + w - 1, 4 * page + w, 133]:
+        for j in (iq - w + 1, iq - w):
+            if 0 <= j < T and iq < T:
+                k[j] = 3.0 * q[iq, ::H // G] / q[iq, ::H // G].norm(dim=-1, keepdim=True) * math.sqrt(d)
+    q, k, v = (t.to(torch.bfloat16) for t in (q, k, v))
+    sinks = 2.0 + torch.randn(H, generator=g)
+    scale = 1.5 / math.sqrt(d)
+    want = plain.attend(q.double(), k.double(), v.double(), scale, cap, window, sinks)
+
+    kv, st = plan_groups({"a": KVPagesNeed(G, d, window)}, 512, page)
+    manager = CacheManager(kv, st, 2)
+    cache = DeviceCache(manager, torch.bfloat16, torch.device("cuda"), 512)
+    step = StepFunction(None, cache, 512, 512)
+    view = cache.view("a")
+    manager.admit("other"); manager.grow("other", 3 * page)       # so that the request's pages are not the first ones
+
+    def run(lo, hi):
+        entries = [StepEntry("r", list(range(lo, hi)), [])]
+        batch = step.build(entries)
+        table = manager.kv_groups[0].table("r")
+        for t in range(lo, hi):
+            view.k[table[t // page], :, t % page] = k[t].cuda()
+            view.v[table[t // page], :, t % page] = v[t].cuda()
+        out = torch.empty(hi - lo, H, d, dtype=torch.bfloat16, device="cuda")
+        paged_attention(q[lo:hi].cuda().contiguous(), out, view, batch, scale=scale, window=window, softcap=cap,
+                        sinks=sinks.cuda())
+        step.finish(entries)
+        step.check_errors()
+        close(out, want[lo:hi], "bfloat16")
+
+    run(0, 133)                  # a portion that ends inside a page
+    run(133, T - n_dec)          # the next one, starting there
+    for t in range(T - n_dec, T):
+        run(t, t + 1)            # single tokens: the decode kernel
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,dk,dv,rank", [(2, 12, 20, 5), (1, 40, 40, 8), (3, 64, 80, 4), (2, 130, 33, 1)])
 def test_gla_decay_recurrence_state_and_output_stage(dtype, H, dk, dv, rank):

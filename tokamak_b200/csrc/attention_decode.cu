@@ -50,6 +50,8 @@ struct DecodeParams {
   int* err;
   int n_items, n_reqs, n_q_heads, n_kv_heads, page_size, max_pages, num_pages, window, n_splits;
   float scale_log2;             // softmax scale * log2(e)
+  float cap_log2, inv_cap;      // score cap * log2(e) (0: none) and scale / cap
+  const float* sinks;           // [n_q_heads] or null: a term of every softmax denominator
 };
 
 template <int D, int STAGES>
@@ -189,7 +191,7 @@ attn_decode_split_kernel(DecodeParams p) {
       for (int e = 0; e < 4; ++e) {
         const int key = tile * kDecTile + nt * 8 + 2 * t4 + (e & 1);
         const bool valid = key >= lo && key <= pos;
-        s[nt][e] = valid ? s[nt][e] * p.scale_log2 : -INFINITY;
+        s[nt][e] = valid ? capped_score_log2(s[nt][e], p.scale_log2, p.cap_log2, p.inv_cap) : -INFINITY;
         mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
       }
     }
@@ -277,7 +279,7 @@ attn_decode_split_kernel(DecodeParams p) {
     }
     if (p.n_splits == 1) {
       // the only block of this (token, kv head): its sums are the result
-      const float inv = 1.0f / l_all;
+      const float inv = 1.0f / (l_all + sink_term_log2(p.sinks, hkv * group + row, m_all));
       p.out[((size_t)tok * p.n_q_heads + (size_t)hkv * group + row) * D + col] = __float2bfloat16_rn(acc * inv);
     } else {
       const size_t pidx = ((size_t)item * p.n_q_heads + (size_t)hkv * group + row) * p.n_splits + split;
@@ -340,7 +342,7 @@ attn_decode_split_kernel(DecodeParams p) {
       l_all += l_loc[k] * m_loc[k];
     }
     l_all = warp_sum(l_all);
-    const float inv = 1.0f / l_all;
+    const float inv = 1.0f / (l_all + sink_term_log2(p.sinks, hkv * group + row, m_all));
 #pragma unroll
     for (int k = 0; k < kDecMaxSplits / 32; ++k) {
       const int s2 = k * 32 + lane;
@@ -407,6 +409,8 @@ struct DecodeBalParams {
   int* err;
   int n_items, n_reqs, n_q_heads, n_kv_heads, page_size, max_pages, num_pages, window;
   float scale_log2;
+  float cap_log2, inv_cap;      // as in DecodeParams
+  const float* sinks;
 };
 
 // The block that holds tile t of the sequence of T tiles: the largest c with T c / G <= t.
@@ -598,7 +602,7 @@ attn_decode_balanced_kernel(DecodeBalParams p) {
         for (int e = 0; e < 4; ++e) {
           const int key = tile * kDecTile + nt * 8 + 2 * t4 + (e & 1);
           const bool valid = key >= lo && key <= pos;
-          s[nt][e] = valid ? s[nt][e] * p.scale_log2 : -INFINITY;
+          s[nt][e] = valid ? capped_score_log2(s[nt][e], p.scale_log2, p.cap_log2, p.inv_cap) : -INFINITY;
           mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
         }
       }
@@ -682,7 +686,7 @@ attn_decode_balanced_kernel(DecodeBalParams p) {
         l_all += sml[(w * 16 + row) * 2 + 1] * f;
       }
       if (whole) {
-        p.out[((size_t)tok * p.n_q_heads + (size_t)hkv * group + row) * D + col] = __float2bfloat16_rn(acc / l_all);
+        p.out[((size_t)tok * p.n_q_heads + (size_t)hkv * group + row) * D + col] = __float2bfloat16_rn(acc / (l_all + sink_term_log2(p.sinks, hkv * group + row, m_all)));
       } else {
         part[row * D + col] = acc;
         if (col == 0) { part[16 * D + row * 2] = m_all; part[16 * D + row * 2 + 1] = l_all; }
@@ -732,7 +736,7 @@ attn_decode_balanced_kernel(DecodeBalParams p) {
             sf[row * n_c + c] = f;
           }
           l_all = warp_sum(l_all);
-          const float inv = 1.0f / l_all;
+          const float inv = 1.0f / (l_all + sink_term_log2(p.sinks, hkv * group + row, m_all));
           __syncwarp();
           for (int c = lane; c < n_c; c += 32) sf[row * n_c + c] *= inv;
         }
@@ -838,7 +842,8 @@ TK_API int tk_attention_decode(const void* q, void* out, const void* k_cache, co
                                const int* tok_req, const int* req_slot, const int* block_table,
                                int* err, int n_items, int n_reqs, int n_q_heads, int n_kv_heads,
                                int head_dim, int page_size, int max_pages, int num_pages, int window,
-                               int n_splits, float scale, cudaStream_t stream) {
+                               int n_splits, float scale, float softcap, const float* sinks,
+                               cudaStream_t stream) {
   if (n_items <= 0) return 0;
   const int group = n_kv_heads > 0 ? n_q_heads / n_kv_heads : 0;
   if (n_kv_heads < 1 || n_q_heads % n_kv_heads != 0 || group > 16 || page_size % 16 != 0 ||
@@ -859,6 +864,9 @@ TK_API int tk_attention_decode(const void* q, void* out, const void* k_cache, co
   p.page_size = page_size; p.max_pages = max_pages; p.num_pages = num_pages; p.window = window;
   p.n_splits = n_splits;
   p.scale_log2 = scale * 1.4426950408889634f;
+  p.cap_log2 = softcap > 0.0f ? softcap * 1.4426950408889634f : 0.0f;
+  p.inv_cap = softcap > 0.0f ? scale / softcap : 0.0f;
+  p.sinks = sinks;
   if (head_dim == 128) return tk::launch_decode<128>(p, stream);
   return tk::launch_decode<64>(p, stream);
 }
@@ -875,7 +883,8 @@ TK_API int tk_attention_decode_balanced(const void* q, void* out, const void* k_
                                         const int* tok_req, const int* req_slot, const int* block_table,
                                         int* err, int n_items, int n_reqs, int n_q_heads, int n_kv_heads,
                                         int head_dim, int page_size, int max_pages, int num_pages, int window,
-                                        int blocks, float scale, cudaStream_t stream) {
+                                        int blocks, float scale, float softcap, const float* sinks,
+                                        cudaStream_t stream) {
   if (n_items <= 0) return 0;
   const int group = n_kv_heads > 0 ? n_q_heads / n_kv_heads : 0;
   if (n_kv_heads < 1 || n_q_heads % n_kv_heads != 0 || group > 16 || page_size % 16 != 0 || blocks < 1 ||
@@ -890,6 +899,9 @@ TK_API int tk_attention_decode_balanced(const void* q, void* out, const void* k_
   p.n_items = n_items; p.n_reqs = n_reqs; p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads;
   p.page_size = page_size; p.max_pages = max_pages; p.num_pages = num_pages; p.window = window;
   p.scale_log2 = scale * 1.4426950408889634f;
+  p.cap_log2 = softcap > 0.0f ? softcap * 1.4426950408889634f : 0.0f;
+  p.inv_cap = softcap > 0.0f ? scale / softcap : 0.0f;
+  p.sinks = sinks;
   if (head_dim == 128) return tk::launch_decode_balanced<128>(p, blocks, stream);
   return tk::launch_decode_balanced<64>(p, blocks, stream);
 }

@@ -80,6 +80,8 @@ struct AttnTcParams {
   int* part_count;               // [(split * n_q_heads + head) * 2 + tile] zero between launches
   int n_records, n_q_heads, n_kv_heads, page_size, max_pages, num_pages, window;
   float scale_log2;
+  float cap_log2, inv_cap;       // score cap * log2(e) (0: none) and scale / cap
+  const float* sinks;            // [n_q_heads] or null: a term of every softmax denominator
 };
 
 struct AttnItem {        // what a block's roles need of an item
@@ -630,7 +632,18 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             mx = fmaxf(mx, sv[c]);
           }
         }
-        mx *= p.scale_log2;       // -inf stays -inf
+        // With a cap the scores are bounded here, cap * tanh(scale * s / cap), and are in units of
+        // log2 from then on (tanh is monotonic: the maximum is the bounded raw maximum).
+        const bool capped = p.cap_log2 != 0.0f;
+        const float eff_scale = capped ? 1.0f : p.scale_log2;
+        if (capped) {
+#pragma unroll
+          for (int c = 0; c < kAtBN; ++c) {
+            if (sv[c] != -INFINITY) sv[c] = capped_score_log2(sv[c], p.scale_log2, p.cap_log2, p.inv_cap);
+          }
+          if (mx != -INFINITY) mx = capped_score_log2(mx, p.scale_log2, p.cap_log2, p.inv_cap);
+        }
+        mx *= eff_scale;          // -inf stays -inf
         const float m_new = fmaxf(m_ref, mx);
         const bool need = m_new > m_ref + kAtRescale;     // also true when the first visible key arrives
         TL_AFTER(__float_as_uint(m_new));
@@ -658,7 +671,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
         const float m_use = (m_ref == -INFINITY) ? 0.0f : m_ref;
         float2 psum = make_float2(0.0f, 0.0f);
-        const float2 scale2 = make_float2(p.scale_log2, p.scale_log2), shift2 = make_float2(-m_use, -m_use);
+        const float2 scale2 = make_float2(eff_scale, eff_scale), shift2 = make_float2(-m_use, -m_use);
 #pragma unroll
         for (int c = 0; c < kAtBN; c += 2) {
           const float2 x = fma2(make_float2(sv[c], sv[c + 1]), scale2, shift2);
@@ -703,7 +716,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       if (row == 0) tl_value(30, 30 + t, (unsigned)it.index);
       if (it.n_parts == 1) {
         if (my_kt > 0) {
-          const float inv = (row_valid && l_sum > 0.0f) ? 1.0f / l_sum : 0.0f;
+          const float inv = (row_valid && l_sum > 0.0f) ? 1.0f / (l_sum + sink_term_log2(p.sinks, it.head, m_ref)) : 0.0f;
           __nv_bfloat16* orow = p.out + ((size_t)(it.tok0 + t * kAtBM + row) * p.n_q_heads + it.head) * D;
 #pragma unroll
           for (int c = 0; c < D / 32; ++c) {
@@ -819,7 +832,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
           for (int i = 0; i < 8; ++i) if (l[i] > 0.0f) l_all += l[i] * exp2f(m[i] - m_all);
         }
-        const float inv = l_all > 0.0f ? 1.0f / l_all : 0.0f;
+        const float inv = l_all > 0.0f ? 1.0f / (l_all + sink_term_log2(p.sinks, it.head, m_all)) : 0.0f;
         const float w_own = l_own > 0.0f ? exp2f(m_ref - m_all) * inv : 0.0f;
         __nv_bfloat16* orow = p.out + ((size_t)(it.tok0 + t * kAtBM + row) * p.n_q_heads + it.head) * D;
 #pragma unroll 1
@@ -938,7 +951,8 @@ TK_API int tk_attention_prefill_tc(const void* q, void* out, const void* k_cache
                                    const int* records, const int* block_table, int* err, int* sched,
                                    float* part_o, float* part_ml, int* part_count, int n_tokens, int n_records,
                                    int n_q_heads, int n_kv_heads, int head_dim, int page_size, int max_pages,
-                                   int num_pages, int window, float scale, cudaStream_t stream) {
+                                   int num_pages, int window, float scale, float softcap, const float* sinks,
+                                   cudaStream_t stream) {
   if (n_records <= 0) return 0;
   if (!tk_attention_prefill_tc_takes(n_q_heads, n_kv_heads, head_dim, page_size) || n_q_heads > 65535 ||
       (long long)n_records * n_q_heads > 0x3fffffffLL) {
@@ -979,6 +993,9 @@ TK_API int tk_attention_prefill_tc(const void* q, void* out, const void* k_cache
   p.n_records = n_records; p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads;
   p.page_size = page_size; p.max_pages = max_pages; p.num_pages = num_pages; p.window = window;
   p.scale_log2 = scale * 1.4426950408889634f;
+  p.cap_log2 = softcap > 0.0f ? softcap * 1.4426950408889634f : 0.0f;
+  p.inv_cap = softcap > 0.0f ? scale / softcap : 0.0f;
+  p.sinks = sinks;
   const long long n_items = (long long)n_records * n_q_heads;
   const int blocks = (int)(n_items < sms[dev] ? n_items : sms[dev]);
   if (head_dim == 128) return tk::launch_prefill_tc<128>(mq, mk, mv, p, blocks, stream);

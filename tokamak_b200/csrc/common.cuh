@@ -85,6 +85,21 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
   return r;
 }
 
+// A scaled score in units of log2(e), optionally bounded by cap * tanh(score / cap):
+// cap_log2 = cap * log2(e) (0: no cap), inv_cap = scale / cap.  tanh(x) = 1 - 2 / (exp(2x) + 1) with
+// the fast exponential and division (absolute error of a few 1e-7): exp overflows to +inf for
+// large x and the quotient is then 0, so the bound is reached exactly.
+__device__ __forceinline__ float capped_score_log2(float dot, float scale_log2, float cap_log2, float inv_cap) {
+  if (cap_log2 == 0.0f) return dot * scale_log2;
+  const float t = __expf(2.0f * dot * inv_cap);
+  return cap_log2 * (1.0f - __fdividef(2.0f, t + 1.0f));
+}
+
+// What a sink adds to a softmax denominator whose terms are 2^(score_log2 - m): 2^(sink log2(e) - m).
+__device__ __forceinline__ float sink_term_log2(const float* sinks, int head, float m) {
+  return sinks != nullptr ? exp2f(sinks[head] * 1.4426950408889634f - m) : 0.0f;
+}
+
 // Programmatic dependent launch.  Every kernel of this library is launched so that it may
 // start while the kernel before it in the stream is still running, lets the kernel after it
 // start early in turn (pdl_trigger at its top), and calls pdl_wait before it touches anything

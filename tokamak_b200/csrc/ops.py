@@ -377,6 +377,13 @@ def attention_plain(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v
            "attention_plain")
 
 
+def _want_sinks(sinks: torch.Tensor | None, n_q_heads: int) -> None:
+    if sinks is not None:
+        _want(sinks, torch.float32, "sinks")
+        if sinks.numel() != n_q_heads:
+            raise KernelError("one sink per query head is needed")
+
+
 def _parts_of(x: torch.Tensor, like: torch.dtype, name: str):
     """(tensor | None, partial sums | None, number of parts, tokens, row length) of a product's
     result: a 2-D tensor in the activation type, or 3-D float32 partial sums."""
@@ -559,8 +566,11 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, 
                      items: torch.Tensor, positions: torch.Tensor, tok_req: torch.Tensor,
                      req_slot: torch.Tensor, block_table: torch.Tensor, err: torch.Tensor, *,
                      scale: float, window: int | None, n_splits: int,
-                     scratch: torch.Tensor | None = None) -> None:
-    """Split-K paged attention for the single next tokens listed in ``items`` (bfloat16 only)."""
+                     scratch: torch.Tensor | None = None, softcap: float | None = None,
+                     sinks: torch.Tensor | None = None) -> None:
+    """Split-K paged attention for the single next tokens listed in ``items`` (bfloat16 only).
+    ``softcap`` and ``sinks`` as in :func:`attention_plain`."""
+    _want_sinks(sinks, q.shape[1])
     _want(q, torch.bfloat16, "q"); _want(out, torch.bfloat16, "out")
     _want(k_cache, torch.bfloat16, "k_cache"); _want(v_cache, torch.bfloat16, "v_cache")
     _want(items, torch.int32, "items")
@@ -584,7 +594,8 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, 
                                          positions.data_ptr(), tok_req.data_ptr(), req_slot.data_ptr(),
                                          block_table.data_ptr(), err.data_ptr(), n_items,
                                          req_slot.numel(), hq, hkv, d, page_size, block_table.shape[1],
-                                         num_pages, int(window or 0), n_splits, float(scale), _stream()),
+                                         num_pages, int(window or 0), n_splits, float(scale),
+                                         float(softcap or 0.0), _ptr(sinks), _stream()),
            "attention_decode")
 
 
@@ -633,9 +644,12 @@ def decode_uses_balanced(device: torch.device, n_items: int, n_kv_heads: int, ma
 def attention_decode_balanced(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                               items: torch.Tensor, positions: torch.Tensor, tok_req: torch.Tensor,
                               req_slot: torch.Tensor, block_table: torch.Tensor, err: torch.Tensor, *,
-                              scale: float, window: int | None, blocks: int) -> None:
+                              scale: float, window: int | None, blocks: int, softcap: float | None = None,
+                              sinks: torch.Tensor | None = None) -> None:
     """Paged attention for the single next tokens listed in ``items`` (bfloat16 only), the key tiles of
-    all (token, kv head) pairs dealt out evenly over ``blocks`` blocks."""
+    all (token, kv head) pairs dealt out evenly over ``blocks`` blocks.  ``softcap`` and ``sinks`` as in
+    :func:`attention_plain`."""
+    _want_sinks(sinks, q.shape[1])
     _want(q, torch.bfloat16, "q"); _want(out, torch.bfloat16, "out")
     _want(k_cache, torch.bfloat16, "k_cache"); _want(v_cache, torch.bfloat16, "v_cache")
     _want(items, torch.int32, "items")
@@ -659,7 +673,8 @@ def attention_decode_balanced(q: torch.Tensor, out: torch.Tensor, k_cache: torch
                                             positions.data_ptr(), tok_req.data_ptr(), req_slot.data_ptr(),
                                             block_table.data_ptr(), err.data_ptr(), n_items, req_slot.numel(),
                                             hq, hkv, d, page_size, block_table.shape[1], num_pages,
-                                            int(window or 0), blocks, float(scale), _stream()),
+                                            int(window or 0), blocks, float(scale), float(softcap or 0.0),
+                                            _ptr(sinks), _stream()),
            "attention_decode_balanced")
 
 
@@ -781,7 +796,8 @@ def _prefill_tc_workspace(device: torch.device, part_slots: int, counters: int, 
 
 def attention_prefill_tc(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                          items: PrefillItems, block_table: torch.Tensor, err: torch.Tensor, *,
-                         scale: float, window: int | None) -> None:
+                         scale: float, window: int | None, softcap: float | None = None,
+                         sinks: torch.Tensor | None = None) -> None:
     """Paged flash attention on tcgen05 for the work list ``items`` (see :func:`prefill_tc_records`),
     a persistent kernel that deals the items out to one block per SM.  Loads whole pages: the cache
     must have been written by :func:`rope_kv` with ``req_q_len`` and ``req_kv_len`` given.  One call
@@ -804,7 +820,8 @@ def attention_prefill_tc(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tens
                                           ws["sched"].data_ptr(), part_o, part_ml, ws["count"].data_ptr(),
                                           n, items.records.shape[0], hq, hkv, d, page_size,
                                           block_table.shape[1], num_pages, int(window or 0),
-                                          float(scale), _stream()), "attention_prefill_tc")
+                                          float(scale), float(softcap or 0.0), _ptr(sinks), _stream()),
+           "attention_prefill_tc")
 
 
 def sm_count(device: torch.device) -> int:

@@ -287,10 +287,13 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, cache_view, step, *, sca
     bf16 = q.dtype == torch.bfloat16
     n_dec = step.decode_items.numel()
     n_pf = step.prefill_items.numel()
-    # the tiled kernels take heads of one size for keys and values, and neither cap nor sinks
-    plain_only = cache_view.v.shape[3] != d or softcap is not None or sinks is not None
-    dec_tiled = bf16 and n_dec > 0 and not plain_only and ops.decode_kernel_takes(hq, hkv, d, page)
-    pf_tiled = bf16 and n_pf > 0 and not plain_only and ops.prefill_kernel_takes(hq, hkv, d, page)
+    # the tiled kernels take heads of one size for keys and values; of the two prefill kernels the
+    # tcgen05 one knows caps and sinks
+    same_size = cache_view.v.shape[3] == d
+    extras = softcap is not None or sinks is not None
+    dec_tiled = bf16 and n_dec > 0 and same_size and ops.decode_kernel_takes(hq, hkv, d, page)
+    pf_tiled = (bf16 and n_pf > 0 and same_size and ops.prefill_kernel_takes(hq, hkv, d, page)
+                and (not extras or ops.prefill_tc_kernel_takes(hq, hkv, d, page)))
     # In a mixed step the two kernels touch different tokens.  One portion against a long context
     # is few blocks (one per pair of 128-row query tiles and head), so the decode kernel runs
     # beside it on a second stream instead of after it.
@@ -304,17 +307,19 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, cache_view, step, *, sca
             if ops.decode_uses_balanced(q.device, n_dec, hkv, step.max_kv_len):
                 ops.attention_decode_balanced(q, out, cache_view.k, cache_view.v, step.decode_items, step.positions,
                                               step.tok_req, step.req_slot, cache_view.table, step.err, scale=scale,
-                                              window=window,
+                                              window=window, softcap=softcap, sinks=sinks,
                                               blocks=ops.decode_balanced_blocks(q.device, n_dec, hkv, step.max_kv_len))
             else:
                 ops.attention_decode(q, out, cache_view.k, cache_view.v, step.decode_items, step.positions,
                                      step.tok_req, step.req_slot, cache_view.table, step.err, scale=scale,
-                                     window=window, n_splits=ops.decode_splits(n_dec, hkv, step.max_kv_len))
+                                     window=window, softcap=softcap, sinks=sinks,
+                                     n_splits=ops.decode_splits(n_dec, hkv, step.max_kv_len))
             if beside:
                 join.record()
     if pf_tiled and ops.prefill_tc_kernel_takes(hq, hkv, d, page):
         ops.attention_prefill_tc(q, out, cache_view.k, cache_view.v, step.prefill_tc,
-                                 cache_view.table, step.err, scale=scale, window=window)
+                                 cache_view.table, step.err, scale=scale, window=window, softcap=softcap,
+                                 sinks=sinks)
     elif pf_tiled:
         ops.attention_prefill(q, out, cache_view.k, cache_view.v, step.prefill_tiles,
                               step.req_q_start, step.req_q_len, step.req_kv_len, step.req_slot,
