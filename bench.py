@@ -780,6 +780,207 @@ def decode_timeline(batch: int, layers: int, ctx: int) -> int:
     return 0
 
 
+
+# ------------------------------------------------------------------------------------------------
+# --design ketalix: the Ketalix design beside a Qwen3 model of equal layer sizes
+
+KETALIX_SIZES = {
+    # width, query / key-value heads of 128 (keys and values), feed-forward, window; the gla layers have
+    # width / 256 heads with keys of 128 and values of 256 (q, k: width / 2; v, gate: width)
+    "2b": dict(width=2048, heads=16, kv_heads=4, dim=128, ff=8192, window=1024, vocab=65536, layers=8),
+    "8b": dict(width=4096, heads=32, kv_heads=8, dim=128, ff=12288, window=1024, vocab=151936, layers=8),
+}
+
+
+def ketalix_config(s: dict) -> dict:
+    """Attention and gla layers in turn, every layer with a feed-forward."""
+    attn = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["dim"],
+            "scale": s["dim"] ** -0.5 * 8.0, "softcap": 30.0, "mask": {"size": s["window"]},
+            "rot": {"base": 1e6, "dims": s["dim"]}, "v_mix": True}
+    gla = {"heads": s["width"] // 256, "dim": 128, "vdim": 256, "tau": 16.0, "rank": 16}
+    mlp = {"kind": "dense", "ff": s["ff"]}
+    layers = [{"type": "attention" if i % 2 == 0 else "gla", "mixer": attn if i % 2 == 0 else gla, "mlp": mlp}
+              for i in range(s["layers"])]
+    return {"architecture": "Ketalix", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-6},
+            "embedding": {"scale": 1.0}, "layers": layers}
+
+
+def qwen3_twin(s: dict) -> dict:
+    """A Qwen3 configuration of the same widths, head counts, feed-forward, depth and window."""
+    return dict(QWEN3_8B, num_hidden_layers=s["layers"], hidden_size=s["width"], num_attention_heads=s["heads"],
+                num_key_value_heads=s["kv_heads"], head_dim=s["dim"], intermediate_size=s["ff"],
+                vocab_size=s["vocab"], use_sliding_window=True, sliding_window=s["window"], max_window_layers=0)
+
+
+def _time_us(run, iters: int = 20) -> float:
+    import torch
+    for _ in range(3):
+        run()
+    torch.cuda.synchronize()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    begin.record()
+    for _ in range(iters):
+        run()
+    end.record()
+    torch.cuda.synchronize()
+    return begin.elapsed_time(end) * 1e3 / iters
+
+
+def ketalix_kernels(s: dict, tokens: int, batch: int, ctx: int, peaks: dict) -> list[dict]:
+    """Every kernel of the design alone, beside the like kernel of the Qwen3 path at the same shape:
+    time, achieved bytes or flops per second, and the fraction of the measured peak."""
+    import torch
+    from tokamak_b200.csrc import ops
+    dev = "cuda"
+    gen = torch.Generator(device=dev).manual_seed(0)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+    err = torch.zeros(4, dtype=torch.int32, device=dev)
+    hq, hkv, d, page, win, width, ff = s["heads"], s["kv_heads"], s["dim"], 16, s["window"], s["width"], s["ff"]
+    bf = lambda *shape: torch.randn(shape, device=dev, generator=gen).bfloat16()
+    rows = []
+
+    def row(kernel, like, us, us_like, nbytes=0, flops=0.0, note=""):
+        r = {"kernel": kernel, "like": like, "us": round(us, 1), "like_us": round(us_like, 1) if us_like else None}
+        for name, t in (("", us), ("like_", us_like)):
+            if not t:
+                continue
+            if flops:
+                r[name + "bf16_frac"] = round(flops / (t * 1e-6) / 1e12 / peaks["bf16_tflops"], 4)
+            elif nbytes:
+                r[name + "hbm_frac"] = round(nbytes / (t * 1e-6) / 1e9 / peaks["hbm_gbs"], 4)
+        if note:
+            r["note"] = note
+        rows.append(r)
+
+    sinks = torch.randn(hq, device=dev, generator=gen)
+    # ---- attention over a prompt of `tokens` tokens, and over `batch` single tokens at context `ctx`
+    pages_pf = -(-tokens // page)
+    kc, vc = bf(pages_pf, hkv, page, d), bf(pages_pf, hkv, page, d)
+    table = torch.randperm(pages_pf, device=dev, generator=gen).to(torch.int32).view(1, pages_pf)
+    q = bf(tokens, hq, d)
+    out = torch.empty_like(q)
+    rec, n_parts, n_split = ops.prefill_tc_records([0], [tokens], [tokens], [0], heads=hq, sms=ops.sm_count(q.device))
+    items = ops.PrefillItems(torch.from_numpy(rec).to(dev), n_parts, n_split)
+    pf = lambda **kw: ops.attention_prefill_tc(q, out, kc, vc, items, table, err, scale=d ** -0.5, window=win, **kw)
+    keys = sum(min(i + 1, win) for i in range(tokens))
+    row("attention, prompt (cap + sink)", "attention, prompt", _time_us(lambda: pf(softcap=30.0, sinks=sinks)),
+        _time_us(pf), flops=4.0 * keys * hq * d,
+        note="three exponential-unit operations a score (tanh by exp and reciprocal, then exp) against one")
+    pages_req = -(-ctx // page)
+    kc, vc = bf(batch * pages_req, hkv, page, d), bf(batch * pages_req, hkv, page, d)
+    table = torch.randperm(batch * pages_req, device=dev, generator=gen).to(torch.int32).view(batch, pages_req)
+    qd = bf(batch, hq, d)
+    outd = torch.empty_like(qd)
+    it, pos = i32(list(range(batch))), i32([ctx - 1] * batch)
+    n_splits = ops.decode_splits(batch, hkv, min(ctx, win))
+    scratch = torch.empty(batch * hq * n_splits * (d + 2), dtype=torch.float32, device=dev)
+    dec = lambda **kw: ops.attention_decode(qd, outd, kc, vc, it, pos, it, it, table, err, scale=d ** -0.5,
+                                            window=win, n_splits=n_splits, scratch=scratch, **kw)
+    row("attention, single tokens (cap + sink)", "attention, single tokens",
+        _time_us(lambda: dec(softcap=30.0, sinks=sinks)), _time_us(dec),
+        nbytes=batch * 2 * hkv * min(ctx, win) * d * 2 + 2 * qd.numel() * 2)
+    # ---- rotation, norm of q and k, page write
+    qkv = bf(tokens, (hq + 2 * hkv) * d)
+    kc, vc = torch.zeros((pages_pf, hkv, page, d), dtype=torch.bfloat16, device=dev), torch.zeros((pages_pf, hkv, page, d), dtype=torch.bfloat16, device=dev)
+    positions, zeros = torch.arange(tokens, dtype=torch.int32, device=dev), torch.zeros(tokens, dtype=torch.int32, device=dev)
+    table = torch.arange(pages_pf, dtype=torch.int32, device=dev).view(1, pages_pf)
+    inv_freq = (1.0 / (1e6 ** (torch.arange(0, d, 2, dtype=torch.float32) / d))).to(dev)
+    rot = ops.rope_table(positions, inv_freq)
+    ones, slot0, len_n = torch.ones(d, device=dev), i32([0]), i32([tokens])
+    vf, lam = torch.randn(tokens, hkv * d, device=dev, generator=gen), torch.full((1,), 0.3, device=dev)
+    pairs = lambda: ops.qkv_pairs(qkv, q, kc, vc, positions, zeros, slot0, table, rot, err, n_q_heads=hq,
+                                  n_kv_heads=hkv, rotary_dim=d, unit_norm_eps=1e-6, v_first_in=vf, v_lambda=lam,
+                                  req_q_len=len_n, req_kv_len=len_n)
+    halves = lambda: ops.rope_kv(qkv, q, kc, vc, positions, zeros, slot0, table, ones, ones, rot, err, n_q_heads=hq,
+                                 n_kv_heads=hkv, head_dim=d, rotary_dim=d, eps=1e-6, req_q_len=len_n, req_kv_len=len_n)
+    nb = qkv.numel() * 2 + q.numel() * 2 + 2 * tokens * hkv * d * 2
+    row("pair rotation + unit norm + value blend + page write", "half rotation + weighted norm + page write",
+        _time_us(pairs), _time_us(halves), nbytes=nb + vf.numel() * 4)
+    # ---- norms around a sublayer
+    resid, branch = torch.randn(tokens, width, device=dev, generator=gen), bf(tokens, width)
+    w1, w2, w3 = (torch.ones(width, device=dev) for _ in range(3))
+    normed = torch.empty(tokens, width, dtype=torch.bfloat16, device=dev)
+    row("output norm + layer scale + residual + input norm", "residual + input norm",
+        _time_us(lambda: ops.branch_norm_add(resid, branch, w1, w2, 1e-6, w3, normed, 1e-6)),
+        _time_us(lambda: ops.add_rmsnorm(resid, branch, w3, normed, 1e-6)), nbytes=tokens * width * (2 + 8 + 2))
+    # ---- the gated unit's activation
+    gu, act = bf(tokens, 2 * ff), torch.empty(tokens, ff, dtype=torch.bfloat16, device=dev)
+    row("gelu gate", "silu gate (the unfused kernel)",
+        _time_us(lambda: ops.swiglu(gu, act, block=ops.SWIGLU_TILE_BLOCK, activation="gelu_tanh")),
+        _time_us(lambda: ops.swiglu(gu, act, block=ops.SWIGLU_TILE_BLOCK)), nbytes=3 * tokens * ff * 2,
+        note="Qwen3 applies silu in its products' epilogues; the gelu gate runs as a kernel of its own")
+    # ---- gated linear attention
+    gh, gk, gv, rank = width // 256, 128, 256, 16
+    rowlen = 2 * gh * gk + 2 * gh * gv + rank
+    for name, n, n_req in (("prompt", tokens, 1), ("single tokens", batch, batch)):
+        proj = bf(n, rowlen) * 0.5
+        w2a, bias = bf(gh * gk, rank) * 0.1, torch.randn(gh * gk, device=dev, generator=gen)
+        state = torch.zeros(max(n_req, 1), gh, gk, gv, device=dev)
+        starts, lens = i32([i * (n // n_req) for i in range(n_req)]), i32([n // n_req] * n_req)
+        slots = i32(list(range(n_req)))
+        prepare = lambda: ops.gla_prepare(proj, 0, gh * gk, 2 * gh * gk, 2 * gh * gk + 2 * gh * gv, w2a, bias, heads=gh,
+                                          key_dim=gk, value_dim=gv, tau=16.0, q_scale=gk ** -0.5)
+        prep = prepare()
+        scan = lambda: ops.gla_scan(prep, state, starts, lens, slots, err)
+        o = scan()
+        us = _time_us(scan)
+        state_bytes = 2 * n_req * gh * gk * gv * 4
+        in_bytes = prep.numel() * 4 + n * gh * gv * 4
+        r = {"kernel": f"gla recurrence, {name}", "like": None, "us": round(us, 1),
+             "hbm_frac": round((state_bytes + in_bytes) / (us * 1e-6) / 1e9 / peaks["hbm_gbs"], 4),
+             "fp32_tflops": round(4.0 * n * gh * gk * gv / (us * 1e-6) / 1e12, 2),
+             "note": "float32 on the CUDA cores, token by token: bound by the length of the chain of tokens in "
+                     "a prompt, by the state's bytes for single tokens"}
+        rows.append(r)
+        nw = torch.ones(gv, device=dev)
+        row(f"gla float32 inputs (scaled q, k, decays, v), {name}", None, _time_us(prepare), 0.0,
+            nbytes=n * (2 * gh * gk + gh * gv + rank) * 2 + prep.numel() * 4)
+        row(f"gla output norm + gate, {name}", None,
+            _time_us(lambda: ops.gla_out(o, proj, 2 * gh * gk + gh * gv, nw, 1e-6, torch.bfloat16)), 0.0,
+            nbytes=n * gh * gv * (4 + 2 + 2))
+    assert err.tolist()[0] == 0
+    return rows
+
+
+def design_compare(args) -> int:
+    """Prefill and decode throughput of the Ketalix design beside a Qwen3 model of equal layer sizes
+    (random weights), and the design's kernels alone beside their like kernels."""
+    import torch
+    from tokamak_b200.engine.core import random_core
+    s = KETALIX_SIZES[args.design_sizes]
+    peaks = load_peaks()
+    ctx, pf_tokens, batch = args.seq_len, args.prefill_tokens, args.batch
+    global PROMPT_PORTION
+    PROMPT_PORTION = args.prompt_tokens or pf_tokens
+    sampler = ClockSampler(torch.cuda.current_device())
+    sampler.start()
+    models = {}
+    for name, raw, vocab in (("ketalix", ketalix_config(s), s["vocab"]), ("qwen3_twin", qwen3_twin(s), s["vocab"])):
+        core = random_core(raw, seed=0, std=0.02, dtype="bfloat16", max_seq_len=max(ctx, pf_tokens), page_size=16,
+                           pool_tokens=max(batch * ctx, pf_tokens + 64), max_slots=batch,
+                           max_step_tokens=max(pf_tokens, batch * ctx))
+        dec = time_decode(core, batch, args.steps, args.warmup, ctx, vocab)
+        one = time_decode(core, 1, args.steps, args.warmup, ctx, vocab)
+        pf_ms = time_prefill(core, vocab, pf_tokens)
+        models[name] = {
+            "decode_tok_s": round(dec["tok_s"], 1), "decode_ms_per_step": round(dec["ms_per_step"], 4),
+            "decode_b1_tok_s": round(one["tok_s"], 1), "prefill_tok_s": round(pf_tokens / (pf_ms / 1e3), 1),
+            "prefill_ms": round(pf_ms, 3), "checked": bool(dec["checked"] and one["checked"]),
+            "graph_replays": dec["graph_replays"], "launches": dec["launches"],
+            "weight_gb": round(weight_bytes(core) / 1e9, 3),
+            "decode_hbm_frac": round((weight_bytes(core) + dec["kv_bytes"]) / (dec["ms_per_step"] / 1e3) / 1e9
+                                     / peaks["hbm_gbs"], 4)}
+        del core
+        torch.cuda.empty_cache()
+    kernels = ketalix_kernels(s, pf_tokens, batch, ctx, peaks)
+    clocks = sampler.stop()
+    print(json.dumps({"design": "Ketalix", "sizes": {**s, "name": args.design_sizes}, "batch": batch, "seq_len": ctx,
+                      "prefill_tokens": pf_tokens, "steps": args.steps, "warmup": args.warmup, "dtype": "bf16",
+                      "data": "synthetic: seeded random weights, uniform random token ids", "models": models,
+                      "kernels": kernels, "peaks": peaks, "clocks": clocks}))
+    return 0 if all(m["checked"] for m in models.values()) else 1
+
+
 def reference_main(args) -> int:
     """``--impl reference``: the unmodified reference from ``baseline/_ref`` on the same metric, or
     one line that says why it cannot run.  Everything it does is in ``baseline/reference_arm.py``."""
@@ -843,6 +1044,10 @@ def main() -> int:
     ap.add_argument("--sizes", default="8b", choices=["0.6b", "8b", "14b", "32b"],
                     help="layer sizes: of --workload (0.6b, 8b), or of the decode/prefill run (8b, the metric's "
                          "own, 14b, 32b)")
+    ap.add_argument("--design", default=None, choices=["ketalix"],
+                    help="measure another design instead: its prefill and decode throughput beside a Qwen3 model of "
+                         "equal layer sizes, and its kernels alone beside their like kernels (--design-sizes)")
+    ap.add_argument("--design-sizes", default="2b", choices=sorted(KETALIX_SIZES))
     ap.add_argument("--num-requests", type=int, default=32)
     ap.add_argument("--max-new-cap", type=int, default=256)
     ap.add_argument("--kv-pool-tokens", type=int, default=16384)
@@ -861,6 +1066,9 @@ def main() -> int:
         return 2
     warmup = max(3, args.warmup)
     steps = max(1, args.steps)
+    if args.design is not None:
+        args.warmup, args.steps = warmup, steps
+        return design_compare(args)
     if args.kernel == "decode_timeline":
         return decode_timeline(args.batch, args.layers or 3, args.ctx)
     if args.kernel == "tcgen05_probe":

@@ -314,28 +314,39 @@ def test_gla_decay_recurrence_state_and_output_stage(dtype, H, dk, dv, rank):
     a_off = 2 * H * dk + 2 * H * dv
     z = x[:, a_off:] @ w2.double().T + bias.double()
     alpha = torch.sigmoid(z).pow(1 / 4.0).view(T, H, dk)
-    la = ops.gla_decay(dev(proj), a_off, dev(w2), dev(bias), 4.0)
-    close(la.exp(), alpha.reshape(T, H * dk), "float32")
+    dks, dvs = ops.gla_prepared_row(dk, dv)
+    prepare = lambda x_in: ops.gla_prepare(x_in, 0, H * dk, 2 * H * dk, a_off, dev(w2), dev(bias), heads=H, key_dim=dk,
+                                           value_dim=dv, tau=4.0, q_scale=dk ** -0.5)
+    prep = prepare(dev(proj))
+    qs = x[:, :H * dk].view(T, H, dk) * dk ** -0.5
+    ks = x[:, H * dk:2 * H * dk].view(T, H, dk)
+    vs = x[:, 2 * H * dk:2 * H * dk + H * dv].view(T, H, dv)
+    close(prep[..., :dk], qs, "float32")
+    close(prep[..., dks:dks + dk], ks, "float32")
+    close(prep[..., 2 * dks:2 * dks + dk], alpha, "float32")
+    close(prep[..., 3 * dks:3 * dks + dv], vs, "float32")
+    for lo, hi in ((dk, dks), (dks + dk, 2 * dks), (2 * dks + dk, 3 * dks), (3 * dks + dv, 3 * dks + dvs)):
+        assert not prep[..., lo:hi].any()                  # the padding to 16 bytes is zero
     # parts of a split product give the same
-    la2 = ops.gla_decay(dev(torch.stack([proj.float() * 0.5, proj.float() * 0.5])), a_off, dev(w2), dev(bias), 4.0)
-    close(la2, la.cpu(), "float32")
+    halves = dev(torch.stack([proj.float() * 0.5, proj.float() * 0.5]))
+    assert torch.equal(prepare(halves), prep)
     state0 = torch.randn(4, H, dk, dv, generator=g)
     state = dev(state0.clone())
     starts = [0, lens[0], lens[0] + lens[1]]
     err = torch.zeros(4, dtype=torch.int32, device="cuda")
-    o = ops.gla_scan(dev(proj), 0, H * dk, 2 * H * dk, la, state, dev(torch.tensor(starts, dtype=torch.int32)),
-                     dev(torch.tensor(lens, dtype=torch.int32)), dev(torch.tensor(slots, dtype=torch.int32)), err,
-                     q_scale=dk ** -0.5, dtype=TORCH[dtype])
+    rows = [dev(torch.tensor(v, dtype=torch.int32)) for v in (starts, lens, slots)]
+    o = ops.gla_scan(prep, state, *rows, err)
     assert err.cpu().tolist()[0] == 0
-    qs = x[:, :H * dk].view(T, H, dk) * dk ** -0.5
-    ks = x[:, H * dk:2 * H * dk].view(T, H, dk)
-    vs = x[:, 2 * H * dk:2 * H * dk + H * dv].view(T, H, dv)
-    alpha32 = la.cpu().double().exp().view(T, H, dk)
+    alpha32 = prep[..., 2 * dks:2 * dks + dk].cpu().double()
     for s, n, slot in zip(starts, lens, slots):
         want_o, want_s = plain.gla_recurrence(qs[s:s + n], ks[s:s + n], vs[s:s + n], alpha32[s:s + n], state0[slot].double())
         close(o[s:s + n], want_o, "float32", scale=10.0)
         close(state[slot], want_s, "float32", scale=10.0)
     assert torch.equal(state[1].cpu(), state0[1])          # a slot of no request is left alone
+    for cols in (32, 16, 8):                               # every split of the columns over blocks, bit for bit
+        again = dev(state0.clone())
+        o2 = ops.gla_scan(prep, again, *rows, err, cols=cols)
+        assert torch.equal(o2, o) and torch.equal(again, state)
     w = 1 + 0.2 * torch.randn(dv, generator=g)
     y = ops.gla_out(o, dev(proj), 2 * H * dk + H * dv, dev(w), 1e-5, TORCH[dtype])
     gate = x[:, 2 * H * dk + H * dv:a_off].view(T, H, dv)
@@ -347,22 +358,24 @@ def test_gla_recurrence_is_bit_equal_however_the_tokens_are_cut():
     from tokamak_b200.csrc import ops
     H, dk, dv, T = 2, 48, 40, 67
     g = torch.Generator().manual_seed(5)
-    proj = dev(torch.randn(T, 2 * H * dk + H * dv, generator=g))
-    la = dev(-torch.rand(T, H * dk, generator=g) * 0.3)
+    prep = torch.randn(T, H, 3 * dk + dv, generator=g)
+    prep[..., 2 * dk:3 * dk] = torch.exp(-torch.rand(T, H, dk, generator=g) * 0.3)
+    prep = dev(prep)
     err = torch.zeros(4, dtype=torch.int32, device="cuda")
     i32 = lambda *v: dev(torch.tensor(v, dtype=torch.int32))
 
-    def run(cuts):
+    def run(cuts, cols=0):
         state = torch.zeros(1, H, dk, dv, device="cuda")
         outs, at = [], 0
         for n in cuts:
-            outs.append(ops.gla_scan(proj[at:at + n].contiguous(), 0, H * dk, 2 * H * dk, la[at:at + n].contiguous(),
-                                     state, i32(0), i32(n), i32(0), err, q_scale=1.0, dtype=torch.float32))
+            outs.append(ops.gla_scan(prep[at:at + n].contiguous(), state, i32(0), i32(n), i32(0), err, cols=cols))
             at += n
         return torch.cat(outs), state
     o1, s1 = run([T])
-    o2, s2 = run([2, 7, 1, 1, 16, 8, 9, 23])
-    assert torch.equal(o1, o2) and torch.equal(s1, s2)
+    for cols in (0, 8, 16, 32):
+        o2, s2 = run([2, 7, 1, 1, 16, 8, 9, 23], cols)
+        assert torch.equal(o1, o2) and torch.equal(s1, s2)
+    assert err.cpu().tolist()[0] == 0
 
 
 # ======================================================================= whole models

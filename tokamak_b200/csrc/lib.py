@@ -41,9 +41,9 @@ _SIGNATURES: dict[str, list] = {
     "tk_qkv_pairs": [_P, _P, c_int, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
                      c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                      c_float, c_int, _P],
-    "tk_gla_decay": [_P, _P, c_int, c_int, c_int, _P, _P, _P, c_int, c_int, c_int, c_float, c_int, _P],
-    "tk_gla_scan": [_P, _P, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P, _P, _P, _P,
-                    c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, _P],
+    "tk_gla_prepare": [_P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, c_int, c_int, c_int, c_int, c_int,
+                       c_float, c_float, c_int, _P],
+    "tk_gla_scan": [_P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P],
     "tk_gla_out": [_P, _P, _P, c_int, c_int, c_int, _P, _P, c_int, c_int, c_int, c_float, c_int, _P],
     "tk_attention_decode": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
                             c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,

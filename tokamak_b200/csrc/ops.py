@@ -470,48 +470,59 @@ def qkv_pairs(qkv: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor, v_c
                                   float(unit_norm_eps or 0.0), dtype_code(q_out.dtype), _stream()), "qkv_pairs")
 
 
-def gla_decay(proj: torch.Tensor, a_off: int, w2: torch.Tensor, bias: torch.Tensor | None, tau: float) -> torch.Tensor:
-    """``log(sigmoid(a W2^T + bias)) / tau`` in float32 ``[tokens, channels]``, where ``a`` are the
-    ``rank`` columns of ``proj`` from ``a_off`` on (``proj``: activation type or partial sums)."""
+def gla_prepared_row(key_dim: int, value_dim: int) -> tuple[int, int]:
+    """``(dks, dvs)``: key and value sizes rounded up to 16 bytes of float32, as :func:`gla_prepare` lays a row out."""
+    return (key_dim + 3) // 4 * 4, (value_dim + 3) // 4 * 4
+
+
+def gla_prepare(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, a_off: int, w2: torch.Tensor,
+                bias: torch.Tensor | None, *, heads: int, key_dim: int, value_dim: int, tau: float,
+                q_scale: float) -> torch.Tensor:
+    """The recurrence's inputs in float32, a row ``q * q_scale | k | alpha | v`` of
+    ``3 dks + dvs`` numbers per (token, head) (see :func:`gla_prepared_row`; the padding is zero), from
+    the columns of the stacked projection ``proj`` (activation type, or float32 partial sums):
+    ``alpha = sigmoid(a W2^T + bias) ** (1 / tau)`` with ``a`` the ``rank`` columns from ``a_off`` on."""
     _want(w2, None, "w2")
     channels, rank = w2.shape
+    if channels != heads * key_dim:
+        raise KernelError("the decay projection must have heads * key_dim rows")
     x, parts, n_parts, n, row = _parts_of(proj, w2.dtype, "proj")
-    if a_off < 0 or a_off + rank > row:
-        raise KernelError("the low-rank columns lie outside the row")
+    for off, size in ((q_off, heads * key_dim), (k_off, heads * key_dim), (v_off, heads * value_dim), (a_off, rank)):
+        if off < 0 or off + size > row:
+            raise KernelError("a column range lies outside the row")
     if bias is not None:
         _want(bias, torch.float32, "bias")
         if bias.numel() != channels:
             raise KernelError("one bias per channel is needed")
-    out = torch.empty((n, channels), dtype=torch.float32, device=w2.device)
-    _check(_lib().tk_gla_decay(_ptr(x), _ptr(parts), n_parts, row, a_off, w2.data_ptr(), _ptr(bias), out.data_ptr(),
-                                  n, channels, rank, float(tau), dtype_code(w2.dtype), _stream()), "gla_decay")
+    dks, dvs = gla_prepared_row(key_dim, value_dim)
+    out = torch.empty((n, heads, 3 * dks + dvs), dtype=torch.float32, device=w2.device)
+    _check(_lib().tk_gla_prepare(_ptr(x), _ptr(parts), n_parts, row, q_off, k_off, v_off, a_off, w2.data_ptr(),
+                                    _ptr(bias), out.data_ptr(), n, heads, key_dim, value_dim, rank, float(tau),
+                                    float(q_scale), dtype_code(w2.dtype), _stream()), "gla_prepare")
     return out
 
 
-def gla_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, log_alpha: torch.Tensor, state: torch.Tensor,
-             req_q_start: torch.Tensor, req_q_len: torch.Tensor, req_slot: torch.Tensor, err: torch.Tensor, *,
-             q_scale: float, dtype: torch.dtype) -> torch.Tensor:
-    """The recurrence ``S = diag(alpha) S + k v^T, o = S^T (q_scale q)`` over every request's tokens of
-    the step; ``state`` is float32 ``[slots, heads, key_dim, value_dim]`` and is advanced in place.
-    Returns ``o`` float32 ``[tokens, heads, value_dim]``."""
-    _want(state, torch.float32, "state"); _want(log_alpha, torch.float32, "log_alpha")
+def gla_scan(prep: torch.Tensor, state: torch.Tensor, req_q_start: torch.Tensor, req_q_len: torch.Tensor,
+             req_slot: torch.Tensor, err: torch.Tensor, *, cols: int = 0) -> torch.Tensor:
+    """The recurrence ``S = diag(alpha) S + k v^T, o = S^T q`` over every request's tokens of the
+    step, from the rows of :func:`gla_prepare`; ``state`` is float32 ``[slots, heads, key_dim, value_dim]``
+    and is advanced in place.  Returns ``o`` float32 ``[tokens, heads, value_dim]``.  ``cols`` is the
+    number of value channels a block takes (32, 16 or 8; 0 lets the kernel's launcher cover the SMs);
+    the result is the same bit for bit under every split."""
+    _want(state, torch.float32, "state"); _want(prep, torch.float32, "prep")
     n_slots, heads, dk, dv = state.shape
-    x, parts, n_parts, n, row = _parts_of(proj, dtype, "proj")
-    if log_alpha.shape != (n, heads * dk):
-        raise KernelError("log_alpha must be [tokens, heads * key_dim]")
-    for off, size in ((q_off, heads * dk), (k_off, heads * dk), (v_off, heads * dv)):
-        if off < 0 or off + size > row:
-            raise KernelError("a column range lies outside the row")
-    if dk > 512:
-        raise KernelError(f"key size {dk} is beyond the kernel's limit of 512")
+    dks, dvs = gla_prepared_row(dk, dv)
+    if prep.dim() != 3 or prep.shape[1:] != (heads, 3 * dks + dvs):
+        raise KernelError("prep must be [tokens, heads, 3 dks + dvs] as gla_prepare returns it")
+    if dk > 256:
+        raise KernelError(f"key size {dk} is beyond the kernel's limit of 256")
     for name, t in (("req_q_start", req_q_start), ("req_q_len", req_q_len), ("req_slot", req_slot)):
         _want(t, torch.int32, name)
-    n_reqs = req_slot.numel()
+    n, n_reqs = prep.shape[0], req_slot.numel()
     out = torch.empty((n, heads, dv), dtype=torch.float32, device=state.device)
-    _check(_lib().tk_gla_scan(_ptr(x), _ptr(parts), n_parts, row, q_off, k_off, v_off, log_alpha.data_ptr(),
-                                 state.data_ptr(), out.data_ptr(), req_q_start.data_ptr(), req_q_len.data_ptr(),
-                                 req_slot.data_ptr(), err.data_ptr(), n, n_reqs, n_slots, heads, dk, dv,
-                                 float(q_scale), dtype_code(dtype), _stream()), "gla_scan")
+    _check(_lib().tk_gla_scan(prep.data_ptr(), state.data_ptr(), out.data_ptr(), req_q_start.data_ptr(),
+                                 req_q_len.data_ptr(), req_slot.data_ptr(), err.data_ptr(), n, n_reqs, n_slots, heads,
+                                 dk, dv, int(cols), _stream()), "gla_scan")
     return out
 
 

@@ -50,8 +50,8 @@ class GatedLinearAttention:
     The state ``[heads, key_dim, value_dim]`` is a float32 record in the request's slot of the
     cache (:class:`~tokamak_b200.cache.manager.StateNeed`): cleared when the slot is handed out,
     read at the start of a step's portion and stored at its end.  The five input projections are
-    one stacked operand, so a step is one product, the decay kernel, the recurrence, the output
-    stage and the output product.  Decays, state, recurrence and norm are float32 in every dtype.
+    one stacked operand, so a step is one product, the kernel that lays out the
+    recurrence's float32 inputs (scaled q, k, decays, v), the recurrence, the output stage and the output product.  Decays, state, recurrence and norm are float32 in every dtype.
     """
 
     GRAPH_SAFE = True
@@ -94,9 +94,9 @@ class GatedLinearAttention:
     def forward(self, h, step, cache_view):
         spec = self.spec
         proj = linear(h, self.w_in, err=step.err)
-        log_alpha = ops.gla_decay(proj, self.a_off, self.w_decay, self.decay_bias, spec.decay_tau)
-        o = ops.gla_scan(proj, self.q_off, self.k_off, self.v_off, log_alpha, cache_view.records,
-                         step.req_q_start, step.req_q_len, step.req_slot, step.err,
-                         q_scale=spec.key_dim ** -0.5, dtype=h.dtype)
+        prep = ops.gla_prepare(proj, self.q_off, self.k_off, self.v_off, self.a_off, self.w_decay, self.decay_bias,
+                               heads=spec.num_heads, key_dim=spec.key_dim, value_dim=spec.value_dim,
+                               tau=spec.decay_tau, q_scale=spec.key_dim ** -0.5)
+        o = ops.gla_scan(prep, cache_view.records, step.req_q_start, step.req_q_len, step.req_slot, step.err)
         y = ops.gla_out(o, proj, self.g_off, self.norm_w, spec.norm_eps, h.dtype)
         return linear(y, self.w_o, err=step.err)
