@@ -321,12 +321,14 @@ def test_gla_decay_recurrence_state_and_output_stage(dtype, H, dk, dv, rank):
     qs = x[:, :H * dk].view(T, H, dk) * dk ** -0.5
     ks = x[:, H * dk:2 * H * dk].view(T, H, dk)
     vs = x[:, 2 * H * dk:2 * H * dk + H * dv].view(T, H, dv)
-    close(prep[..., :dk], qs, "float32")
-    close(prep[..., dks:dks + dk], ks, "float32")
-    close(prep[..., 2 * dks:2 * dks + dk], alpha, "float32")
-    close(prep[..., 3 * dks:3 * dks + dv], vs, "float32")
-    for lo, hi in ((dk, dks), (dks + dk, 2 * dks), (2 * dks + dk, 3 * dks), (3 * dks + dv, 3 * dks + dvs)):
-        assert not prep[..., lo:hi].any()                  # the padding to 16 bytes is zero
+    pieces, values = ops.gla_prepared_views(prep, H, dk, dv)
+    pieces = pieces.permute(1, 0, 3, 2, 4).reshape(T, H, 3, dks)          # [token, head, q / k / alpha, channel]
+    values = values.permute(1, 0, 2)
+    close(pieces[:, :, 0, :dk], qs, "float32")
+    close(pieces[:, :, 1, :dk], ks, "float32")
+    close(pieces[:, :, 2, :dk], alpha, "float32")
+    close(values[..., :dv], vs, "float32")
+    assert not pieces[..., dk:].any() and not values[..., dv:].any()      # the padding to 16 bytes is zero
     # parts of a split product give the same
     halves = dev(torch.stack([proj.float() * 0.5, proj.float() * 0.5]))
     assert torch.equal(prepare(halves), prep)
@@ -337,7 +339,7 @@ def test_gla_decay_recurrence_state_and_output_stage(dtype, H, dk, dv, rank):
     rows = [dev(torch.tensor(v, dtype=torch.int32)) for v in (starts, lens, slots)]
     o = ops.gla_scan(prep, state, *rows, err)
     assert err.cpu().tolist()[0] == 0
-    alpha32 = prep[..., 2 * dks:2 * dks + dk].cpu().double()
+    alpha32 = pieces[:, :, 2, :dk].cpu().double()
     for s, n, slot in zip(starts, lens, slots):
         want_o, want_s = plain.gla_recurrence(qs[s:s + n], ks[s:s + n], vs[s:s + n], alpha32[s:s + n], state0[slot].double())
         close(o[s:s + n], want_o, "float32", scale=10.0)
@@ -358,9 +360,12 @@ def test_gla_recurrence_is_bit_equal_however_the_tokens_are_cut():
     from tokamak_b200.csrc import ops
     H, dk, dv, T = 2, 48, 40, 67
     g = torch.Generator().manual_seed(5)
-    prep = torch.randn(T, H, 3 * dk + dv, generator=g)
-    prep[..., 2 * dk:3 * dk] = torch.exp(-torch.rand(T, H, dk, generator=g) * 0.3)
-    prep = dev(prep)
+    pieces = torch.randn(H, T, dk // 4, 3, 4, generator=g)
+    pieces[..., 2, :] = torch.exp(-torch.rand(H, T, dk // 4, 4, generator=g) * 0.3)
+    values = torch.randn(H, T, dv, generator=g)
+
+    def prepared(at, n):       # the layout of gla_prepare for the tokens at .. at + n
+        return dev(torch.cat([pieces[:, at:at + n].reshape(-1), values[:, at:at + n].reshape(-1)]))
     err = torch.zeros(4, dtype=torch.int32, device="cuda")
     i32 = lambda *v: dev(torch.tensor(v, dtype=torch.int32))
 
@@ -368,7 +373,7 @@ def test_gla_recurrence_is_bit_equal_however_the_tokens_are_cut():
         state = torch.zeros(1, H, dk, dv, device="cuda")
         outs, at = [], 0
         for n in cuts:
-            outs.append(ops.gla_scan(prep[at:at + n].contiguous(), state, i32(0), i32(n), i32(0), err, cols=cols))
+            outs.append(ops.gla_scan(prepared(at, n), state, i32(0), i32(n), i32(0), err, cols=cols))
             at += n
         return torch.cat(outs), state
     o1, s1 = run([T])

@@ -18,6 +18,7 @@
 // activation type, or float32 partial sums [parts, tokens, row_stride] of a split-K product).
 #include "common.cuh"
 #include "mma_utils.cuh"
+#include "tcgen05_utils.cuh"
 
 namespace tk {
 
@@ -37,9 +38,12 @@ __device__ __forceinline__ float gla_ld(const GlaInput& in, size_t off) {
   return acc;
 }
 
-// What the recurrence reads, float32 whatever the engine's dtype: a row per (token, head) of
-//   q * q_scale [dks] | k [dks] | alpha [dks] | v [dvs]
-// with dks = key_dim and dvs = value_dim rounded up to a multiple of 4 (16 bytes), the padding zero,
+// What the recurrence reads, float32 whatever the engine's dtype, head by head so that a head's
+// tokens lie one after the other and a batch of them is one bulk copy:
+//   [heads][tokens][dks / 4 pieces of  q * q_scale [4] | k [4] | alpha [4]  (four key channels each)]
+//   [heads][tokens][v [dvs]]
+// with dks = key_dim and dvs = value_dim rounded up to a multiple of 4 (16 bytes), the padding zero;
+// a thread of the recurrence finds its four rows' inputs in one stretch of 48 bytes;
 // and alpha = sigmoid(sum_j a[t, j] w2[c, j] + bias[c]) ^ (1 / tau), computed through its logarithm
 // log(sigmoid(z)) = min(z, 0) - log1p(exp(-|z|)).  One thread per element.
 template <typename T>
@@ -55,29 +59,34 @@ __global__ void gla_prepare_kernel(GlaInput in, int q_off, int k_off, int v_off,
   const int e = (int)(idx - th * per);
   const int t = (int)(th / heads), h = (int)(th - (long long)t * heads);
   const size_t row = (size_t)t * in.row_stride;
-  float* out = prep + (size_t)th * (3 * dks + dvs);
+  const size_t ht = (size_t)h * n_tokens + t;
   if (e >= dks) {
     const int c = e - dks;
-    out[3 * dks + c] = c < dv ? gla_ld<T>(in, row + v_off + h * dv + c) : 0.0f;
+    prep[(size_t)heads * n_tokens * 3 * dks + ht * dvs + c] = c < dv ? gla_ld<T>(in, row + v_off + h * dv + c) : 0.0f;
     return;
   }
-  if (e >= dk) { out[e] = 0.0f; out[dks + e] = 0.0f; out[2 * dks + e] = 0.0f; return; }
+  float* out = prep + ht * 3 * dks;
+  float* piece = out + (e / 4) * 12 + (e & 3);
+  if (e >= dk) { piece[0] = 0.0f; piece[4] = 0.0f; piece[8] = 0.0f; return; }
   const int ch = h * dk + e;
   float z = 0.0f;
   for (int j = 0; j < rank; ++j) z += gla_ld<T>(in, row + a_off + j) * to_f32<T>(w2[(size_t)ch * rank + j]);
   if (bias != nullptr) z += bias[ch];
-  out[e] = gla_ld<T>(in, row + q_off + ch) * q_scale;
-  out[dks + e] = gla_ld<T>(in, row + k_off + ch);
-  out[2 * dks + e] = expf((fminf(z, 0.0f) - log1pf(expf(-fabsf(z)))) * inv_tau);
+  piece[0] = gla_ld<T>(in, row + q_off + ch) * q_scale;
+  piece[4] = gla_ld<T>(in, row + k_off + ch);
+  piece[8] = expf((fminf(z, 0.0f) - log1pf(expf(-fabsf(z)))) * inv_tau);
 }
 
-constexpr int kGlaRows = 8;       // rows of the state (key channels) that one thread keeps in registers
-constexpr int kGlaBatch = 32;     // tokens staged in shared memory at a time, times the row groups of a warp
-constexpr int kGlaMaxWarps = 16;  // warps of a block
-constexpr int kGlaMaxKey = 256;   // key_dim: 16 warps of 16 rows at 16 columns a block; at 32 columns a block 128
+constexpr int kGlaTile = 4;       // a thread keeps 4 rows (key channels) x 4 columns (value channels) of the state
+constexpr int kGlaMaxWarps = 16;  // working warps of a block
+constexpr int kGlaService = 5;    // serving warps: one copies the inputs in, four add the partial outputs up
+constexpr int kGlaBatch = 8;      // tokens staged in shared memory at a time
+constexpr int kGlaChunk = 16;     // row groups that one lane adds up when the partial outputs are joined
+constexpr int kGlaStages = 4;     // staging buffers: a batch is asked for three batches before it is needed
+constexpr int kGlaMaxKey = 256;   // key_dim: 16 warps of 16 rows at 32 columns a block
 
 struct GlaScanParams {
-  const float* prep;        // [n_tokens, heads, 3 dks + dvs], see gla_prepare_kernel
+  const float* prep;        // [heads, n_tokens, 3 dks] and [heads, n_tokens, dvs], see gla_prepare_kernel
   float* state;             // [n_slots, heads, key_dim, value_dim]
   float* out;               // [n_tokens, heads, value_dim]
   const int* req_q_start;
@@ -87,29 +96,59 @@ struct GlaScanParams {
   int n_tokens, n_slots, heads, key_dim, value_dim, dks, dvs;
 };
 
-// One block per (request, head, kCols value channels).  A warp's lanes are kCols columns times
-// 32 / kCols groups of eight rows; a thread keeps its eight rows of one column of the state in
-// registers and walks the request's tokens in order.  The host picks kCols so that the grid covers
-// the SMs: a prompt alone has only heads * value_dim columns to share out.  Tokens are staged a
-// batch at a time by asynchronous 16-byte copies into one of two buffers in shared memory: while
-// one batch is worked through, the next is on its way (the chain of tokens is what bounds a
-// prompt, so no load may stand in it).  A token's output is the sum of the eight-row groups'
-// partial sums in the order of the rows, whatever kCols is, so the result does not depend on the
-// split.
+// One block per (request, head, kCols value channels); it walks the request's tokens in order.
+//
+// Working warps: a thread keeps a 4 x 4 tile of the state in registers; per token it loads q, k and
+// the decays of its four rows and the values of its four columns (four 16-byte loads of shared
+// memory for 48 multiply-adds; with a column a thread the loads' way back into registers was the
+// bound), two columns an instruction, and leaves its four partial outputs in shared memory.  A
+// warp's lanes are kCols / 4 column groups times 128 / kCols row groups.
+//
+// Five more warps serve them, so that nothing but the recurrence stands in the chain of tokens.
+// One brings the batches of eight tokens into four staging buffers, three batches ahead (a batch
+// is worked through in less time than memory takes to answer): a bulk copy for the q | k | alpha
+// pieces, which reports to the buffer's barrier, and 16-byte asynchronous copies for the values.
+// Four add up the partial outputs of the batch before from the other of two output buffers.  One
+// barrier per batch joins all warps.  A token's output is a sum over rows in an order that follows
+// the rows alone, so the result does not depend on kCols, which the host picks by the number of
+// blocks: a prompt alone has only heads * value_dim columns to share out.
+// size bytes (a multiple of 16, both addresses 16-byte aligned) from global to this block's shared
+// memory by the copy unit; the bytes are counted off at the barrier
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t size, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
+               ::"r"(dst), "l"(src), "r"(size), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void gla_block_barrier() {
+  asm volatile("bar.sync 1, %0;\n" ::"r"((int)blockDim.x) : "memory");
+}
+
 template <int kCols>
-__global__ void __launch_bounds__(kGlaMaxWarps * 32, 1) gla_scan_kernel(GlaScanParams p) {
-  constexpr int kGroups = 32 / kCols;               // row groups of a warp
-  constexpr int kBatch = kGlaBatch / kGroups;       // tokens of a batch
+__global__ void __launch_bounds__((kGlaMaxWarps + kGlaService) * 32, 1) gla_scan_kernel(GlaScanParams p) {
+  constexpr int kColGroups = kCols / kGlaTile;      // column groups of a warp
+  constexpr int kRowGroups = 32 / kColGroups;       // row groups of a warp
+  constexpr int kBatch = kGlaBatch;
   extern __shared__ __align__(16) float smem[];
   pdl_trigger();
   const int r = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * kCols;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
-  const int col = lane % kCols, group = warp * kGroups + lane / kCols, n_groups = n_warps * kGroups;
-  const int dkp = n_groups * kGlaRows;                      // a staged row: key channels, padded with zeros
-  const int per_buf = 3 * kBatch * dkp + kBatch * kCols;    // q, k, alpha [kBatch][dkp] and v [kBatch][kCols]
-  float* so = smem + 2 * per_buf;                           // partial outputs [kBatch][n_groups][kCols]
-  for (int i = threadIdx.x; i < 2 * per_buf; i += blockDim.x) smem[i] = 0.0f;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = (blockDim.x >> 5) - kGlaService;
+  const int n_groups = n_warps * kRowGroups;
+  const int qka_len = 3 * p.dks;                            // a staged token's q | k | alpha pieces
+  const int per_buf = kBatch * (qka_len + kCols);           // staging buffers (stage0 + i * per_buf): the pieces, then the values
+  const int per_out = kBatch * n_groups * kCols;            // partial outputs [kBatch][n_groups][kCols], two of them
+  // the first 32 floats: a barrier per staging buffer, and from the 16th on twelve zeros, the inputs of
+  // rows beyond key_dim's last piece
+  const uint32_t bars = smem_u32(smem);
+  const float* zeros = smem + 16;
+  float* stage0 = smem + 32;
+  float* so = stage0 + kGlaStages * per_buf;
+  for (int i = threadIdx.x; i < 16 + kGlaStages * per_buf; i += blockDim.x) smem[16 + i] = 0.0f;
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kGlaStages; ++i) mbar_init(bars + 8 * i, 1);
+  }
+  fence_async_shared();       // the zeros and the barriers, before the copy unit writes here
   __syncthreads();
+  volatile __shared__ int no_abort;
+  if (threadIdx.x == 0) no_abort = 0;
   pdl_wait();
   const int dk = p.key_dim, dv = p.value_dim;
   const int slot = p.req_slot[r];
@@ -118,96 +157,157 @@ __global__ void __launch_bounds__(kGlaMaxWarps * 32, 1) gla_scan_kernel(GlaScanP
     if (threadIdx.x == 0) set_error(p.err, kErrRequest, r, slot, q0);
     return;
   }
-  const int j = j0 + col;
-  float* srow = p.state + (((size_t)slot * p.heads + h) * dk + (size_t)group * kGlaRows) * dv + j;
-  float2 s[kGlaRows / 2];       // rows in pairs: two multiply-adds an instruction
-#pragma unroll
-  for (int ii = 0; ii < kGlaRows; ++ii) {
-    const float v0 = (j < dv && group * kGlaRows + ii < dk) ? srow[(size_t)ii * dv] : 0.0f;
-    if (ii & 1) s[ii / 2].y = v0; else s[ii / 2].x = v0;
-  }
+  const int n_batches = (n + kBatch - 1) / kBatch;
 
-  // A warp copies the tokens warp, warp + n_warps, ... of a batch, a lane 16 bytes at a time.
-  const int prep_row = 3 * p.dks + p.dvs, chunks = p.dks / 4;
-  auto copy = [&](int t0, float* buf) {
-    const int nb = min(kBatch, n - t0);
-    for (int tb = warp; tb < nb; tb += n_warps) {
-      const float* src = p.prep + ((size_t)(q0 + t0 + tb) * p.heads + h) * prep_row;
-      for (int c = lane; c < chunks; c += 32) {
-#pragma unroll
-        for (int a = 0; a < 3; ++a) {
-          cp_async16(smem_u32(buf + (a * kBatch + tb) * dkp + 4 * c), src + a * p.dks + 4 * c, true);
+  if (warp >= n_warps) {
+    // ---- serving warps
+    const int sw = warp - n_warps, st = (sw - 1) * 32 + lane;      // warp 0 copies, the others add up
+    // Serving warp 0 brings a batch in: the tokens' q | k | alpha pieces lie one after the other in
+    // memory and are one bulk copy that reports to the stage's barrier; the block's values are
+    // 16-byte asynchronous copies, a group a batch (an empty one beyond the last batch).
+    const float* qka = p.prep + ((size_t)h * p.n_tokens + q0) * qka_len;
+    const float* val = p.prep + (size_t)p.heads * p.n_tokens * qka_len + ((size_t)h * p.n_tokens + q0) * p.dvs + j0;
+    auto copy = [&](int b) {
+      if (sw != 0) return;
+      if (b < n_batches) {
+        const int t0 = b * kBatch, nb = min(kBatch, n - t0);
+        float* buf = stage0 + (b % kGlaStages) * per_buf;
+        const uint32_t bar = bars + 8 * (b % kGlaStages);
+        if (lane == 0) {
+          const uint32_t bytes = (uint32_t)(nb * qka_len * sizeof(float));
+          mbar_expect_tx(bar, bytes);
+          bulk_load(smem_u32(buf), qka + (size_t)t0 * qka_len, bytes, bar);
+        }
+        for (int i = lane; i < nb * kColGroups; i += 32) {
+          const int tb = i / kColGroups, c = (i % kColGroups) * kGlaTile;
+          const bool live = j0 + c < p.dvs;
+          cp_async16(smem_u32(buf + kBatch * qka_len + tb * kCols + c), val + (size_t)(t0 + tb) * p.dvs + (live ? c : 0), live);
         }
       }
-      if (lane < kCols / 4) {
-        const bool live = j0 + 4 * lane < p.dvs;
-        cp_async16(smem_u32(buf + 3 * kBatch * dkp + tb * kCols + 4 * lane), src + 3 * p.dks + (live ? j0 + 4 * lane : 0), live);
-      }
-    }
-    cp_async_commit();
-  };
-
-  if (n > 0) copy(0, smem);
-  int cur = 0;
-  for (int t0 = 0; t0 < n; t0 += kBatch) {
-    const int nb = min(kBatch, n - t0);
-    const float* buf = smem + cur * per_buf;
-    cp_async_wait<0>();
-    __syncthreads();          // this batch has landed; everyone is done with the other buffer and with so
-    if (t0 + kBatch < n) copy(t0 + kBatch, smem + (cur ^ 1) * per_buf);
-    const float* sq = buf + group * kGlaRows; const float* sk = sq + kBatch * dkp; const float* sa = sk + kBatch * dkp;
-    const float* sv = buf + 3 * kBatch * dkp + col;
-    // One token: its q, k and decays come from registers that were loaded while the token before was
-    // worked on (the loads of shared memory would otherwise stand in the chain of tokens), and the next
-    // token's are loaded first of all.
-    float4 q[kGlaRows / 4], k[kGlaRows / 4], a[kGlaRows / 4];
-    float v;
-    auto load = [&](int tb) {
-      v = sv[tb * kCols];
-#pragma unroll
-      for (int g = 0; g < kGlaRows / 4; ++g) {
-        q[g] = reinterpret_cast<const float4*>(sq + tb * dkp)[g];
-        k[g] = reinterpret_cast<const float4*>(sk + tb * dkp)[g];
-        a[g] = reinterpret_cast<const float4*>(sa + tb * dkp)[g];
+      cp_async_commit();
+    };
+    // ... and waits for it, with a limit: past it the error is flagged and the block goes on with what it has
+    auto landed = [&](int b) {
+      if (sw != 0) return;
+      cp_async_wait<kGlaStages - 2>();      // all but the last two groups: this batch's values
+      if (b >= n_batches) return;
+      const uint32_t bar = bars + 8 * (b % kGlaStages), parity = (uint32_t)(b / kGlaStages) & 1u;
+      if (!mbar_wait(bar, parity, &no_abort) && !mbar_wait(bar, parity, &no_abort)) {
+        if (lane == 0) set_error(p.err, kErrWait, 40, b, r);
       }
     };
-    auto token = [&](int tb, bool more) {
-      float4 qc[kGlaRows / 4], kc[kGlaRows / 4], ac[kGlaRows / 4];
-      const float vc = v;
+    // Four columns of a token are added up by 1, 2 or 4 neighbouring lanes: a lane takes sixteen row
+    // groups (64 rows) in their order, then the lanes' sums are joined as (0 + 1) + (2 + 3).  The
+    // grouping follows the rows alone, so the sum is the same whatever the block's shape.
+    const int lanes_per = n_groups <= kGlaChunk ? 1 : n_groups <= 2 * kGlaChunk ? 2 : 4;
+    auto reduce = [&](int b) {
+      if (sw == 0) return;
+      const int t0 = b * kBatch, nb = min(kBatch, n - t0);
+      const float* part = so + (b & 1) * per_out;
+      const int items = nb * kColGroups * lanes_per;
+      for (int base = 0; base < items; base += (kGlaService - 1) * 32) {       // whole warps stay together for the shuffles
+        const int idx = base + st;
+        const bool live = idx < items;
+        const int item = live ? idx / lanes_per : 0, piece = idx % lanes_per;
+        const int tb = item / kColGroups, c = (item % kColGroups) * kGlaTile;
+        const int w0 = piece * kGlaChunk, w1 = live ? min(n_groups, w0 + kGlaChunk) : w0;
+        const float4* src = reinterpret_cast<const float4*>(part + tb * n_groups * kCols + c);
+        float4 o = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll 8
+        for (int w = w0; w < w1; ++w) {
+          const float4 x = src[w * (kCols / 4)];
+          o.x += x.x; o.y += x.y; o.z += x.z; o.w += x.w;
+        }
+        for (int d = 1; d < lanes_per; d <<= 1) {
+          o.x += __shfl_xor_sync(0xffffffffu, o.x, d); o.y += __shfl_xor_sync(0xffffffffu, o.y, d);
+          o.z += __shfl_xor_sync(0xffffffffu, o.z, d); o.w += __shfl_xor_sync(0xffffffffu, o.w, d);
+        }
+        if (!live || piece != 0) continue;
+        float* dst = p.out + ((size_t)(q0 + t0 + tb) * p.heads + h) * dv + j0 + c;
+        const float t[kGlaTile] = {o.x, o.y, o.z, o.w};
 #pragma unroll
-      for (int g = 0; g < kGlaRows / 4; ++g) { qc[g] = q[g]; kc[g] = k[g]; ac[g] = a[g]; }
-      if (more) load(tb + 1);
-      const float2 v2 = make_float2(vc, vc);
+        for (int e = 0; e < kGlaTile; ++e) {
+          if (j0 + c + e < dv) dst[e] = t[e];
+        }
+      }
+    };
+    for (int b = 0; b < kGlaStages - 1; ++b) copy(b);
+    landed(0);
+    gla_block_barrier();
+    for (int b = 0; b < n_batches; ++b) {
+      copy(b + kGlaStages - 1);             // into the buffer that batch b - 1 was worked through from
+      if (b > 0) reduce(b - 1);
+      landed(b + 1);
+      gla_block_barrier();                  // batch b is worked through, batch b + 1 has landed
+    }
+    if (n_batches > 0) reduce(n_batches - 1);
+    return;
+  }
+
+  // ---- working warps
+  const int cg = lane % kColGroups, group = warp * kRowGroups + lane / kColGroups;
+  const int row0 = group * kGlaTile, j = j0 + cg * kGlaTile;
+  float* stile = p.state + (((size_t)slot * p.heads + h) * dk + row0) * dv + j;
+  float2 s[kGlaTile][2];        // [row][column pair]
+#pragma unroll
+  for (int rr = 0; rr < kGlaTile; ++rr) {
+    float t[kGlaTile];
+#pragma unroll
+    for (int c = 0; c < kGlaTile; ++c) t[c] = (row0 + rr < dk && j + c < dv) ? stile[(size_t)rr * dv + c] : 0.0f;
+    s[rr][0] = make_float2(t[0], t[1]); s[rr][1] = make_float2(t[2], t[3]);
+  }
+  gla_block_barrier();
+  for (int b = 0; b < n_batches; ++b) {
+    const int nb = min(kBatch, n - b * kBatch);
+    const float* buf = stage0 + (b % kGlaStages) * per_buf;
+    // (the copy unit's writes are seen by whoever has seen the stage's barrier flip: it has, long ago)
+    mbar_wait(bars + 8 * (b % kGlaStages), (uint32_t)(b / kGlaStages) & 1u, &no_abort);
+    // One token: its inputs come from registers that were loaded while the token before was worked
+    // on, and the next token's are loaded first of all.
+    const bool padded = row0 >= p.dks;          // rows beyond the last piece read zeros
+    const float4* mine = reinterpret_cast<const float4*>(padded ? zeros : buf + group * (3 * kGlaTile));
+    const float4* vals = reinterpret_cast<const float4*>(buf + kBatch * qka_len + cg * kGlaTile);
+    const int step = padded ? 0 : qka_len / 4;
+    float4* part = reinterpret_cast<float4*>(so + (b & 1) * per_out + group * kCols + cg * kGlaTile);
+    float4 q, k, a, v;
+    auto load = [&]() {
+      q = mine[0]; k = mine[1]; a = mine[2]; v = vals[0];
+      mine += step; vals += kCols / 4;
+    };
+    auto token = [&](bool more) {
+      const float4 qc = q, kc = k, ac = a;
+      const float2 v01 = make_float2(v.x, v.y), v23 = make_float2(v.z, v.w);
+      if (more) load();
+      const float qs[kGlaTile] = {qc.x, qc.y, qc.z, qc.w}, ks[kGlaTile] = {kc.x, kc.y, kc.z, kc.w},
+                  as[kGlaTile] = {ac.x, ac.y, ac.z, ac.w};
       float2 o01 = make_float2(0.0f, 0.0f), o23 = make_float2(0.0f, 0.0f);
 #pragma unroll
-      for (int g = 0; g < kGlaRows / 4; ++g) {
-        s[2 * g] = fma2(make_float2(ac[g].x, ac[g].y), s[2 * g], mul2(make_float2(kc[g].x, kc[g].y), v2));
-        s[2 * g + 1] = fma2(make_float2(ac[g].z, ac[g].w), s[2 * g + 1], mul2(make_float2(kc[g].z, kc[g].w), v2));
-        o01 = fma2(make_float2(qc[g].x, qc[g].y), s[2 * g], o01);
-        o23 = fma2(make_float2(qc[g].z, qc[g].w), s[2 * g + 1], o23);
+      for (int rr = 0; rr < kGlaTile; ++rr) {
+        const float2 a2 = make_float2(as[rr], as[rr]), k2 = make_float2(ks[rr], ks[rr]), q2 = make_float2(qs[rr], qs[rr]);
+        s[rr][0] = fma2(a2, s[rr][0], mul2(k2, v01));
+        s[rr][1] = fma2(a2, s[rr][1], mul2(k2, v23));
+        o01 = fma2(q2, s[rr][0], o01);
+        o23 = fma2(q2, s[rr][1], o23);
       }
-      so[(tb * n_groups + group) * kCols + col] = (o01.x + o01.y) + (o23.x + o23.y);
+      *part = make_float4(o01.x, o01.y, o23.x, o23.y);
+      part += n_groups * kCols / 4;
     };
-    load(0);
+    load();
     if (nb == kBatch) {       // a full batch: a loop of known length
-#pragma unroll 4
-      for (int tb = 0; tb < kBatch; ++tb) token(tb, tb + 1 < kBatch);
+#pragma unroll
+      for (int tb = 0; tb < kBatch; ++tb) token(tb + 1 < kBatch);
     } else {
-      for (int tb = 0; tb < nb; ++tb) token(tb, tb + 1 < nb);
+      for (int tb = 0; tb < nb; ++tb) token(tb + 1 < nb);
     }
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < nb * kCols; idx += blockDim.x) {
-      const int tb = idx / kCols, c = idx % kCols;
-      if (j0 + c >= dv) continue;
-      float o = 0.0f;
-      for (int w = 0; w < n_groups; ++w) o += so[(tb * n_groups + w) * kCols + c];
-      p.out[((size_t)(q0 + t0 + tb) * p.heads + h) * dv + j0 + c] = o;
-    }
-    cur ^= 1;
+    gla_block_barrier();
   }
 #pragma unroll
-  for (int ii = 0; ii < kGlaRows; ++ii) {
-    if (j < dv && group * kGlaRows + ii < dk) srow[(size_t)ii * dv] = (ii & 1) ? s[ii / 2].y : s[ii / 2].x;
+  for (int rr = 0; rr < kGlaTile; ++rr) {
+    const float t[kGlaTile] = {s[rr][0].x, s[rr][0].y, s[rr][1].x, s[rr][1].y};
+#pragma unroll
+    for (int c = 0; c < kGlaTile; ++c) {
+      if (row0 + rr < dk && j + c < dv) stile[(size_t)rr * dv + c] = t[c];
+    }
   }
 }
 
@@ -246,7 +346,7 @@ static tk::GlaInput gla_input(const void* x, const float* parts, int n_parts, in
   return in;
 }
 
-// prep: float32 [n_tokens, heads, 3 dks + dvs] with dks, dvs = key_dim, value_dim rounded up to a multiple of 4.
+// prep: float32, n_tokens * heads * (3 dks + dvs) numbers with dks, dvs = key_dim, value_dim rounded up to a multiple of 4.
 TK_API int tk_gla_prepare(const void* x, const float* parts, int n_parts, int row_stride, int q_off, int k_off,
                           int v_off, int a_off, const void* w2, const float* bias, float* prep, int n_tokens,
                           int heads, int key_dim, int value_dim, int rank, float tau, float q_scale, int dtype,
@@ -268,19 +368,20 @@ TK_API int tk_gla_prepare(const void* x, const float* parts, int n_parts, int ro
 
 template <int kCols>
 static cudaError_t gla_scan_launch(const tk::GlaScanParams& p, int n_reqs, cudaStream_t stream) {
-  constexpr int kGroups = 32 / kCols, kBatch = tk::kGlaBatch / kGroups;
-  const int n_warps = (p.key_dim + tk::kGlaRows * kGroups - 1) / (tk::kGlaRows * kGroups);
-  const int n_groups = n_warps * kGroups, dkp = n_groups * tk::kGlaRows;
+  constexpr int kRowGroups = 32 / (kCols / tk::kGlaTile), kBatch = tk::kGlaBatch;
+  const int rows_per_warp = kRowGroups * tk::kGlaTile;
+  const int n_warps = (p.key_dim + rows_per_warp - 1) / rows_per_warp;
+  const int n_groups = n_warps * kRowGroups;
   const int col_tiles = (p.value_dim + kCols - 1) / kCols;
   if (n_warps > tk::kGlaMaxWarps || col_tiles > 65535) return cudaErrorInvalidValue;
-  const size_t smem = sizeof(float) * (2 * ((size_t)3 * kBatch * dkp + kBatch * kCols) + (size_t)kBatch * n_groups * kCols);
+  const size_t smem = sizeof(float) * (32 + (size_t)tk::kGlaStages * kBatch * (3 * p.dks + kCols) + (size_t)2 * kBatch * n_groups * kCols);
   cudaError_t e = cudaSuccess;
   if (smem > 48 * 1024) {
     e = cudaFuncSetAttribute(tk::gla_scan_kernel<kCols>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
   }
   return tk::launch(tk::gla_scan_kernel<kCols>, dim3((unsigned)n_reqs, (unsigned)p.heads, (unsigned)col_tiles),
-                    dim3(n_warps * 32), smem, stream, p);
+                    dim3((n_warps + tk::kGlaService) * 32), smem, stream, p);
 }
 
 static int gla_sm_count() {
@@ -295,8 +396,7 @@ static int gla_sm_count() {
   return sms;
 }
 
-// cols: value channels per block (32, 16 or 8), or 0 for the widest split whose grid still has a block
-// for every SM.
+// cols: value channels per block (32, 16 or 8), or 0 for the launcher's choice by the number of blocks.
 TK_API int tk_gla_scan(const float* prep, float* state, float* out, const int* req_q_start, const int* req_q_len,
                        const int* req_slot, int* err, int n_tokens, int n_reqs, int n_slots, int heads, int key_dim,
                        int value_dim, int cols, cudaStream_t stream) {
@@ -313,10 +413,12 @@ TK_API int tk_gla_scan(const float* prep, float* state, float* out, const int* r
   if (cols == 0) {
     const long long sms = gla_sm_count();
     if (sms <= 0) return (int)cudaErrorInvalidDevice;
-    const long long columns = (long long)n_reqs * heads * value_dim;
-    cols = columns >= 32 * sms ? 32 : columns >= 16 * sms ? 16 : 8;
+    // measured on prompts of 2,048 tokens (8 and 16 heads of 128 x 256): 16 columns a block unless that
+    // makes more than two blocks an SM (then 32) or fewer than one for every other SM (then 8)
+    const long long blocks16 = (long long)n_reqs * heads * ((value_dim + 15) / 16);
+    cols = blocks16 > 2 * sms ? 32 : 2 * blocks16 >= sms ? 16 : 8;
   }
-  if (cols == 32 && key_dim > tk::kGlaMaxWarps * tk::kGlaRows) cols = 16;     // eight rows a warp: 128 rows a block
+  if (cols == 32 && key_dim > 128) cols = 16;      // the buffers of 32 columns and 256 rows are more than a block may have
   const cudaError_t e = cols == 32 ? gla_scan_launch<32>(p, n_reqs, stream)
                         : cols == 16 ? gla_scan_launch<16>(p, n_reqs, stream) : gla_scan_launch<8>(p, n_reqs, stream);
   return (int)e;

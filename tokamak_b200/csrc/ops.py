@@ -478,10 +478,11 @@ def gla_prepared_row(key_dim: int, value_dim: int) -> tuple[int, int]:
 def gla_prepare(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, a_off: int, w2: torch.Tensor,
                 bias: torch.Tensor | None, *, heads: int, key_dim: int, value_dim: int, tau: float,
                 q_scale: float) -> torch.Tensor:
-    """The recurrence's inputs in float32, a row ``q * q_scale | k | alpha | v`` of
-    ``3 dks + dvs`` numbers per (token, head) (see :func:`gla_prepared_row`; the padding is zero), from
-    the columns of the stacked projection ``proj`` (activation type, or float32 partial sums):
-    ``alpha = sigmoid(a W2^T + bias) ** (1 / tau)`` with ``a`` the ``rank`` columns from ``a_off`` on."""
+    """The recurrence's inputs in float32 from the columns of the stacked projection ``proj``
+    (activation type, or float32 partial sums), as one flat tensor that :func:`gla_prepared_views`
+    takes apart: ``q * q_scale``, ``k`` and ``alpha = sigmoid(a W2^T + bias) ** (1 / tau)`` (``a``: the
+    ``rank`` columns from ``a_off`` on) in pieces of four key channels, and ``v``; head by head, so
+    that a head's tokens follow one another."""
     _want(w2, None, "w2")
     channels, rank = w2.shape
     if channels != heads * key_dim:
@@ -495,11 +496,21 @@ def gla_prepare(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, a_off: i
         if bias.numel() != channels:
             raise KernelError("one bias per channel is needed")
     dks, dvs = gla_prepared_row(key_dim, value_dim)
-    out = torch.empty((n, heads, 3 * dks + dvs), dtype=torch.float32, device=w2.device)
+    out = torch.empty(n * heads * (3 * dks + dvs), dtype=torch.float32, device=w2.device)
     _check(_lib().tk_gla_prepare(_ptr(x), _ptr(parts), n_parts, row, q_off, k_off, v_off, a_off, w2.data_ptr(),
                                     _ptr(bias), out.data_ptr(), n, heads, key_dim, value_dim, rank, float(tau),
                                     float(q_scale), dtype_code(w2.dtype), _stream()), "gla_prepare")
     return out
+
+
+def gla_prepared_views(prep: torch.Tensor, heads: int, key_dim: int, value_dim: int) -> tuple[torch.Tensor, torch.Tensor]:
+    """``(pieces, values)`` of what :func:`gla_prepare` returned: ``pieces[h, t, i, 0 / 1 / 2, :]`` are
+    ``q * q_scale``, ``k`` and ``alpha`` of the key channels ``4 i .. 4 i + 3``, ``values[h, t, :]`` is ``v``
+    (both padded with zeros up to ``dks``, ``dvs``)."""
+    dks, dvs = gla_prepared_row(key_dim, value_dim)
+    n = prep.numel() // (heads * (3 * dks + dvs))
+    split = heads * n * 3 * dks
+    return prep[:split].view(heads, n, dks // 4, 3, 4), prep[split:].view(heads, n, dvs)
 
 
 def gla_scan(prep: torch.Tensor, state: torch.Tensor, req_q_start: torch.Tensor, req_q_len: torch.Tensor,
@@ -512,13 +523,13 @@ def gla_scan(prep: torch.Tensor, state: torch.Tensor, req_q_start: torch.Tensor,
     _want(state, torch.float32, "state"); _want(prep, torch.float32, "prep")
     n_slots, heads, dk, dv = state.shape
     dks, dvs = gla_prepared_row(dk, dv)
-    if prep.dim() != 3 or prep.shape[1:] != (heads, 3 * dks + dvs):
-        raise KernelError("prep must be [tokens, heads, 3 dks + dvs] as gla_prepare returns it")
+    if prep.dim() != 1 or prep.numel() % (heads * (3 * dks + dvs)) != 0:
+        raise KernelError("prep must be the flat tensor that gla_prepare returns for this state's sizes")
     if dk > 256:
         raise KernelError(f"key size {dk} is beyond the kernel's limit of 256")
     for name, t in (("req_q_start", req_q_start), ("req_q_len", req_q_len), ("req_slot", req_slot)):
         _want(t, torch.int32, name)
-    n, n_reqs = prep.shape[0], req_slot.numel()
+    n, n_reqs = prep.numel() // (heads * (3 * dks + dvs)), req_slot.numel()
     out = torch.empty((n, heads, dv), dtype=torch.float32, device=state.device)
     _check(_lib().tk_gla_scan(prep.data_ptr(), state.data_ptr(), out.data_ptr(), req_q_start.data_ptr(),
                                  req_q_len.data_ptr(), req_slot.data_ptr(), err.data_ptr(), n, n_reqs, n_slots, heads,
