@@ -45,7 +45,7 @@ KX_B = {
 KX_C = {
     "architecture": "Ketalix", "vocab": 300, "width": 128, "norm": {"eps": 1e-6}, "embedding": {"scale": 0.5},
     "layers": [
-        _layer("attention", _attn(4, 2, 64, 64, 0.25, window=40, softcap=12.0, rot=32, v_mix=True), 160),
+        _layer("attention", _attn(4, 2, 64, 64, 0.25, window=40, softcap=12.0, rot=32, v_mix=True), 192),   # blocks of 64: the products apply the gate
         _layer("gla", {"heads": 2, "dim": 64, "vdim": 80, "tau": 16.0, "rank": 4}, None),
         _layer("attention", _attn(4, 2, 64, 64, 0.25, softcap=12.0, rot=64, v_mix=True), 96),
     ],

@@ -738,11 +738,19 @@ def test_gemm_tcgen05_swapped_partials(tokens, n_out, k, splits, cluster):
     torch.testing.assert_close(got, want, rtol=1e-4, atol=1e-3 * (k ** 0.5) / 8)
 
 
+def _gate(g: torch.Tensor, activation: str) -> torch.Tensor:
+    """The gated unit's activation in the argument's precision (silu, or the tanh form of gelu)."""
+    if activation == "silu":
+        return g * torch.sigmoid(g)
+    return 0.5 * g * (1 + torch.tanh((2 / torch.pi) ** 0.5 * (g + 0.044715 * g ** 3)))
+
+
+@pytest.mark.parametrize("activation", ["silu", "gelu_tanh"])
 @pytest.mark.parametrize("tokens,inter,k,splits", [(8, 192, 512, 2), (1, 64, 64, 1), (64, 640, 1536, 6),
                                                     (33, 128, 200, 1), (16, 12288, 4096, 8), (5, 320, 4096, 8)])
-def test_gemm_tcgen05_swapped_with_gated_activation(tokens, inter, k, splits):
+def test_gemm_tcgen05_swapped_with_gated_activation(tokens, inter, k, splits, activation):
     """The decode product of a stacked gate/up weight (rows alternating in blocks of 64) whose
-    cluster stores silu(gate) * up itself, against the separate product and formula."""
+    cluster stores act(gate) * up itself, against the separate product and formula."""
     from tokamak_b200.csrc import ops
     gen = torch.Generator().manual_seed(tokens + inter)
     x = torch.randn(tokens, k, generator=gen).bfloat16()
@@ -751,17 +759,17 @@ def test_gemm_tcgen05_swapped_with_gated_activation(tokens, inter, k, splits):
     b = ops.SWIGLU_TILE_BLOCK
     w = torch.stack((wg.view(inter // b, b, k), wu.view(inter // b, b, k)), dim=1).reshape(2 * inter, k).contiguous()
     err = err_word()
-    got = ops.gemm_tc_swapped(w.to(DEV), x.to(DEV), err, splits, cluster=splits, swiglu=True)
+    got = ops.gemm_tc_swapped(w.to(DEV), x.to(DEV), err, splits, cluster=splits, swiglu=True, activation=activation)
     torch.cuda.synchronize()
     assert err.tolist()[0] == 0, err.tolist()
     assert got.shape == (tokens, inter) and got.dtype == torch.bfloat16
     g, u = x.double() @ wg.double().T, x.double() @ wu.double().T
-    want = g * torch.sigmoid(g) * u
+    want = _gate(g, activation) * u
     torch.testing.assert_close(got.double().cpu(), want, rtol=1e-2, atol=1e-2)
     # the same sums through the float32 partials and the separate activation kernel: bit-equal
     sums = ops.gemm_tc_swapped(w.to(DEV), x.to(DEV), err, splits, cluster=splits)
     two = torch.empty(tokens, inter, device=DEV, dtype=torch.bfloat16)
-    ops.swiglu(sums, two, block=b)
+    ops.swiglu(sums, two, block=b, activation=activation)
     assert torch.equal(two, got)
 
 
@@ -782,9 +790,10 @@ def test_gemm_tcgen05_pairs_of_sms(tokens, n_out, k):
     torch.testing.assert_close(got.double().cpu(), want, rtol=1e-2, atol=2e-2)
 
 
+@pytest.mark.parametrize("activation", ["silu", "gelu_tanh"])
 @pytest.mark.parametrize("tokens,inter,k", [(256, 128, 256), (700, 320, 1536), (2048, 1024, 4096), (65, 64, 72)])
-def test_gemm_tcgen05_pairs_with_gated_activation(tokens, inter, k):
-    """The same product storing silu(gate) * up of a stacked gate/up weight in blocks of 64."""
+def test_gemm_tcgen05_pairs_with_gated_activation(tokens, inter, k, activation):
+    """The same product storing act(gate) * up of a stacked gate/up weight in blocks of 64."""
     from tokamak_b200.csrc import ops
     gen = torch.Generator().manual_seed(tokens + inter)
     x = torch.randn(tokens, k, generator=gen).bfloat16()
@@ -793,12 +802,12 @@ def test_gemm_tcgen05_pairs_with_gated_activation(tokens, inter, k):
     b = ops.SWIGLU_TILE_BLOCK
     w = torch.stack((wg.view(inter // b, b, k), wu.view(inter // b, b, k)), dim=1).reshape(2 * inter, k).contiguous()
     err = err_word()
-    got = ops.gemm_pair(x.to(DEV), w.to(DEV), err, swiglu=True)
+    got = ops.gemm_pair(x.to(DEV), w.to(DEV), err, swiglu=True, activation=activation)
     torch.cuda.synchronize()
     assert err.tolist()[0] == 0, err.tolist()
     assert got.shape == (tokens, inter)
     g, u = x.double() @ wg.double().T, x.double() @ wu.double().T
-    torch.testing.assert_close(got.double().cpu(), g * torch.sigmoid(g) * u, rtol=1e-2, atol=2e-2)
+    torch.testing.assert_close(got.double().cpu(), _gate(g, activation) * u, rtol=1e-2, atol=2e-2)
 
 
 @pytest.mark.parametrize("tokens,hidden,k,splits", [(8, 256, 512, 4), (1, 128, 64, 1), (33, 640, 1536, 8), (64, 4096, 4096, 8)])

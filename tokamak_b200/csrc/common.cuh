@@ -100,6 +100,13 @@ __device__ __forceinline__ float sink_term_log2(const float* sinks, int head, fl
   return sinks != nullptr ? exp2f(sinks[head] * 1.4426950408889634f - m) : 0.0f;
 }
 
+// Activations of the gated unit (the kernel of its own and the products' epilogues): 0 = silu,
+// 1 = the tanh form of gelu, 0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3))).
+__device__ __forceinline__ float glu_act(float g, int act) {
+  if (act == 1) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+  return g / (1.0f + expf(-g));
+}
+
 // Two float32 operations in one instruction (sm_100): kernels that are bound by the
 // instructions they issue (the softmax warps of the tiled attention, the recurrence of gated linear
 // attention) halve their multiply-adds and additions with these.

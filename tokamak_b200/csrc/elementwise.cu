@@ -162,13 +162,6 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const T* __res
   }
 }
 
-// Activations of the gated unit: 0 = silu, 1 = the tanh form of gelu,
-// 0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3))).
-__device__ __forceinline__ float glu_act(float g, int act) {
-  if (act == 1) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
-  return g / (1.0f + expf(-g));
-}
-
 // out[t, j] = act(gate[t, j]) * up[t, j]           (act = silu: src/tokamak/model/layers.py:103)
 // A row of gu holds gate and up alternating in blocks: `block` gate values, then the `block` up
 // values of the same outputs (block = inter: all gate values, then all up values).

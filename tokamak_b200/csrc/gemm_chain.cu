@@ -72,6 +72,7 @@ struct ChainPhase {
   const __nv_bfloat16* x;           // [tokens, k] activations, row stride ld_x elements
   long long ld_x;
   int rows_total, k_total, n_tiles, kb_total, epilogue;
+  int glu_act;                      // gated epilogue: 0 = silu, 1 = the tanh form of gelu
   void* out;                        // plain: float [tokens, rows]; gated: bf16 [tokens, rows / 2]
   const float* colscale_parts;      // [n_colscale_parts, tokens] or null (see gemm_tcgen05.cu)
   int n_colscale_parts;
@@ -596,9 +597,9 @@ gemm_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant_
                 uu.x *= sc; uu.y *= sc; uu.z *= sc; uu.w *= sc;
                 uint2 packed;
                 *reinterpret_cast<__nv_bfloat162*>(&packed.x) =
-                    __floats2bfloat162_rn(g.x / (1.0f + expf(-g.x)) * uu.x, g.y / (1.0f + expf(-g.y)) * uu.y);
+                    __floats2bfloat162_rn(glu_act(g.x, P.glu_act) * uu.x, glu_act(g.y, P.glu_act) * uu.y);
                 *reinterpret_cast<__nv_bfloat162*>(&packed.y) =
-                    __floats2bfloat162_rn(g.z / (1.0f + expf(-g.z)) * uu.z, g.w / (1.0f + expf(-g.w)) * uu.w);
+                    __floats2bfloat162_rn(glu_act(g.z, P.glu_act) * uu.z, glu_act(g.w, P.glu_act) * uu.w);
                 *reinterpret_cast<uint2*>(out + (size_t)c * inter + oc) = packed;
               }
             }
@@ -801,8 +802,10 @@ TK_API int tk_gemm_chain(const TkChainPhaseArgs* phases, int n_phases, int token
   p.n_phases = n_phases; p.bn = bn; p.cols_total = tokens; p.max_tiles = max_tiles;
   p.err = err; p.scratch = scratch; p.counters = counters; p.sync = counters + (size_t)kChMaxPhases * max_tiles;
   for (int i = 0; i < n_phases; ++i) {
-    const TkChainPhaseArgs& a = phases[i];
+    TkChainPhaseArgs a = phases[i];
     ChainPhase& ph = p.phase[i];
+    ph.glu_act = a.epilogue == 4 ? 1 : 0;      // 4: the gated epilogue with the tanh form of gelu
+    if (a.epilogue == 4) a.epilogue = kChSwiglu;
     if (a.rows <= 0 || a.k <= 0 || a.k % 8 != 0 || a.epilogue < kChPlain || a.epilogue > kChQkvRope) {
       return (int)cudaErrorInvalidValue;
     }

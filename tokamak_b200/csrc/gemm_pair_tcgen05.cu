@@ -41,7 +41,7 @@ struct GemmPairParams {
   int* err;
   int rows, cols, k;
   long long ld_out;
-  int mode;                 // 0: bf16 [rows, cols]; 1: gated activation, bf16 [rows, cols / 2]
+  int mode;                 // 0: bf16 [rows, cols]; 1, 2: gated activation (silu, gelu: glu_act(mode - 1)), bf16 [rows, cols / 2]
 };
 
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
@@ -199,7 +199,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       tc_fence_after();
       const int row = tm * 2 * kGpBM + (int)rank * kGpBM + quarter * 32 + lane;
       const uint32_t tacc = tmem_base + lane_addr + (uint32_t)(b * kGpBN);
-      if (p.mode == 1) {
+      if (p.mode != 0) {
         // columns [0, 64) and [128, 192) of the tile are gate values, [64, 128) and [192, 256) the up
         // values of the same outputs
         const int inter = p.cols >> 1;
@@ -222,7 +222,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                 for (int e = 0; e < 4; ++e) {
                   const float g0 = __uint_as_float(g[q * 8 + 2 * e]), g1 = __uint_as_float(g[q * 8 + 2 * e + 1]);
                   const float u0 = __uint_as_float(u[q * 8 + 2 * e]), u1 = __uint_as_float(u[q * 8 + 2 * e + 1]);
-                  h2[e] = __floats2bfloat162_rn(g0 / (1.0f + expf(-g0)) * u0, g1 / (1.0f + expf(-g1)) * u1);
+                  h2[e] = __floats2bfloat162_rn(glu_act(g0, p.mode - 1) * u0, glu_act(g1, p.mode - 1) * u1);
                 }
                 *reinterpret_cast<uint4*>(orow + oc + q * 8) = v;
               }
@@ -295,7 +295,7 @@ static int make_pair_map(CUtensorMap* map, const void* ptr, long long rows, long
 TK_API int tk_gemm_bf16_pair(const void* x, const void* w, void* out, int* err, int rows, int cols, int k,
                              long long ld_x, long long ld_w, long long ld_out, int mode, cudaStream_t stream) {
   if (rows <= 0 || cols <= 0) return 0;
-  if (k <= 0 || k % 8 != 0 || ld_out % 8 != 0 || (mode != 0 && mode != 1) || (mode == 1 && cols % 128 != 0) ||
+  if (k <= 0 || k % 8 != 0 || ld_out % 8 != 0 || mode < 0 || mode > 2 || (mode != 0 && cols % 128 != 0) ||
       ((uintptr_t)out & 15u) != 0) {
     return (int)cudaErrorInvalidValue;
   }

@@ -32,6 +32,7 @@ constexpr int kGtThreads = 192;   // warp 0: TMA, warp 1: MMA, warps 2..5: epilo
 // halves of 64 outputs, and the block that adds the splits up stores
 // bf16(silu(gate) * up) as [token, rows / 2] instead of the float32 sums.
 constexpr int kGtEpiSwiglu = 1;
+constexpr int kGtEpiGeglu = 4;    // asked for at the C interface only: the gated epilogue with glu_act = 1
 // Epilogue for a product that ends a residual branch: the block that adds the
 // splits up adds the sums to the float32 residual stream in place, stores
 // bf16(residual * norm weight) for the product that follows the next RMSNorm, and the tile's
@@ -77,6 +78,7 @@ struct GemmTcParams {
   int n_splits;
   int cluster_reduce;       // 0, or the cluster size: that many consecutive splits of a tile
                             // form a cluster and store their sum as one part (n_splits / cluster parts)
+  int glu_act;              // epilogue 1: the activation of the gate, see glu_act (0 = silu, 1 = gelu, tanh form)
   int epilogue;             // 0 = float32 sums; 1 = gated activation, see kGtEpiSwiglu;
                             // 2 = residual sum and preparation of the next norm, see kGtEpiResidualNorm
   // every column (token) of the sums is multiplied by
@@ -378,9 +380,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_r, const __grid_cons
           }
           uint2 packed;
           *reinterpret_cast<__nv_bfloat162*>(&packed.x) =
-              __floats2bfloat162_rn(g.x / (1.0f + expf(-g.x)) * u.x, g.y / (1.0f + expf(-g.y)) * u.y);
+              __floats2bfloat162_rn(glu_act(g.x, p.glu_act) * u.x, glu_act(g.y, p.glu_act) * u.y);
           *reinterpret_cast<__nv_bfloat162*>(&packed.y) =
-              __floats2bfloat162_rn(g.z / (1.0f + expf(-g.z)) * u.z, g.w / (1.0f + expf(-g.w)) * u.w);
+              __floats2bfloat162_rn(glu_act(g.z, p.glu_act) * u.z, glu_act(g.w, p.glu_act) * u.w);
           *reinterpret_cast<uint2*>(out + (size_t)col * inter + oc) = packed;
         }
       }
@@ -582,7 +584,8 @@ static int launch_gemm(const void* r, const void* c, int rows, int cols, int k, 
 // consumer); parts = n_splits, or n_splits / cluster_reduce when cluster_reduce > 1 (2..8, a divisor
 // of n_splits): that many consecutive splits form a thread-block cluster and store their sum.
 // epilogue = 1 (rows a multiple of 128 whose gate and up rows alternate in blocks of 64, all
-// splits in one cluster): out is bfloat16 [cols, rows / 2] = silu(gate) * up.
+// splits in one cluster): out is bfloat16 [cols, rows / 2] = silu(gate) * up; epilogue = 4: the same with
+// the tanh form of gelu in silu's place.
 // epilogue = 2 (rows a multiple of 128, all splits in one cluster): nothing goes to out; the
 // sums are added to resid [cols, rows] (float32) in place, xb_out [cols, rows] receives
 // bf16(resid * norm_w) and sumsq_out [rows / 128, cols] the tiles' sums of squares of resid.
@@ -596,13 +599,15 @@ TK_API int tk_gemm_bf16_tcgen05(const void* r, const void* c, void* out, int* er
                                 const float* colscale_parts, int n_colscale_parts, float colscale_inv_dim,
                                 float colscale_eps, float* resid, const float* norm_w, void* xb_out,
                                 float* sumsq_out, cudaStream_t stream) {
+  const bool gelu = epilogue == tk::kGtEpiGeglu;
+  if (gelu) epilogue = tk::kGtEpiSwiglu;
   if (epilogue < 0 || epilogue > tk::kGtEpiResidualNorm) return (int)cudaErrorInvalidValue;
   if (epilogue == tk::kGtEpiResidualNorm &&
       (resid == nullptr || norm_w == nullptr || xb_out == nullptr || sumsq_out == nullptr)) {
     return (int)cudaErrorInvalidValue;
   }
   tk::GemmTcParams p = {};
-  p.out = out; p.err = err; p.epilogue = epilogue;
+  p.out = out; p.err = err; p.epilogue = epilogue; p.glu_act = gelu ? 1 : 0;
   p.colscale_parts = colscale_parts; p.n_colscale_parts = n_colscale_parts; p.colscale_inv_dim = colscale_inv_dim;
   p.colscale_eps = colscale_eps; p.resid = resid; p.norm_w = norm_w; p.xb_out = (__nv_bfloat16*)xb_out; p.sumsq_out = sumsq_out;
   return tk::launch_gemm(r, c, rows, cols, k, ld_r, ld_c, bn, n_splits, max_stages, cluster_reduce, p, stream);

@@ -910,7 +910,7 @@ SWIGLU_TILE_BLOCK = 64     # gate/up rows alternate in blocks of this many for t
 
 def gemm_tc_swapped(weight: torch.Tensor, x: torch.Tensor, err: torch.Tensor, n_splits: int,
                     out: torch.Tensor | None = None, max_stages: int = 0, cluster: int = 0,
-                    swiglu: bool = False, colscale: tuple | None = None,
+                    swiglu: bool = False, activation: str = "silu", colscale: tuple | None = None,
                     residual_norm: tuple | None = None, chain: "ProductChain | None" = None):
     """``x @ weight^T`` on tcgen05, the weight being the 128-row operand (for few tokens: every
     weight byte is streamed once by TMA), as float32 partial sums ``[parts, tokens, N_out]`` for
@@ -968,7 +968,9 @@ def gemm_tc_swapped(weight: torch.Tensor, x: torch.Tensor, err: torch.Tensor, n_
             raise KernelError("the fused activation wants rows in blocks of 64 gate + 64 up and one cluster")
         if out is None:
             out = torch.empty((tokens, n_out // 2), dtype=torch.bfloat16, device=x.device)
-        epilogue, out_ptr, result = 1, out.data_ptr(), out
+        if activation not in GLU_ACTIVATIONS:
+            raise KernelError(f"unknown activation {activation!r}")
+        epilogue, out_ptr, result = (1 if activation == "silu" else 4), out.data_ptr(), out
     else:
         if out is None:
             out = torch.empty((parts, tokens, n_out), dtype=torch.float32, device=x.device)
@@ -1220,7 +1222,8 @@ def pair_gemm_takes(tokens: int, n_out: int, k: int, fused: bool = False) -> boo
     return tiles >= PAIR_GEMM_MIN_TILES and k % 8 == 0 and n_out % 8 == 0
 
 
-def gemm_pair(x: torch.Tensor, weight: torch.Tensor, err: torch.Tensor, swiglu: bool = False) -> torch.Tensor:
+def gemm_pair(x: torch.Tensor, weight: torch.Tensor, err: torch.Tensor, swiglu: bool = False,
+              activation: str = "silu") -> torch.Tensor:
     """``x @ weight^T`` for many tokens on pairs of SMs (tcgen05.mma.cta_group::2, persistent grid);
     bfloat16 ``[tokens, N_out]``.  ``swiglu=True``: the weight is a stacked gate/up matrix whose rows
     alternate in blocks of ``SWIGLU_TILE_BLOCK``; the result is ``[tokens, N_out / 2] = silu(gate) * up``."""
@@ -1232,11 +1235,14 @@ def gemm_pair(x: torch.Tensor, weight: torch.Tensor, err: torch.Tensor, swiglu: 
     if swiglu and n_out % (2 * SWIGLU_TILE_BLOCK):
         raise KernelError("the fused activation wants rows in blocks of 64 gate + 64 up")
     width = n_out // 2 if swiglu else n_out
+    if swiglu and activation not in GLU_ACTIVATIONS:
+        raise KernelError(f"unknown activation {activation!r}")
+    mode = 1 + GLU_ACTIVATIONS[activation] if swiglu else 0
     if width % 8:
         raise KernelError("the output width must be a multiple of 8")
     out = torch.empty((tokens, width), dtype=torch.bfloat16, device=x.device)
     _check(_lib().tk_gemm_bf16_pair(x.data_ptr(), weight.data_ptr(), out.data_ptr(), err.data_ptr(), tokens,
-                                       n_out, k, k, k, width, 1 if swiglu else 0, _stream()), "gemm_pair")
+                                       n_out, k, k, k, width, mode, _stream()), "gemm_pair")
     return out
 
 

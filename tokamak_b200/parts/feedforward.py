@@ -36,8 +36,7 @@ class SwiGLU:
     that adds its K splits up applies the activation itself, so that decoding needs no
     activation kernel and no float32 round trip of the ``[tokens, 2I]`` sums.
 
-    With another activation than silu (the tanh form of gelu) the products run unfused and
-    the activation kernel applies it.
+    ``activation`` (silu, or the tanh form of gelu) is applied by the same epilogues.
     """
 
     def __init__(self, spec: SwiGLUSpec, prefix: str, tensors: dict[str, torch.Tensor], rt: Runtime):
@@ -45,7 +44,7 @@ class SwiGLU:
         self.rt = rt
         if spec.activation not in ops.GLU_ACTIVATIONS:
             raise ValueError(f"unknown activation {spec.activation!r}; known: {', '.join(ops.GLU_ACTIVATIONS)}")
-        self.fused_act = spec.activation == "silu"      # the products' fused epilogues apply silu
+        self.fused_act = True      # the products' fused epilogues know every activation of ops.GLU_ACTIVATIONS
         gate, up = tensors[prefix + spec.gate_name], tensors[prefix + spec.up_name]
         i, h = spec.intermediate_size, spec.hidden_size
         b = ops.SWIGLU_TILE_BLOCK
@@ -86,14 +85,14 @@ class SwiGLU:
             if isinstance(h, OwedNorm):
                 colscale, h = (h.sumsq, h.dim, h.eps), h.xb
             act = ops.gemm_tc_swapped(self.w_gate_up, h, err, splits, max_stages=stages, cluster=cluster,
-                                      swiglu=True, colscale=colscale, chain=chain)
+                                      swiglu=True, activation=self.spec.activation, colscale=colscale, chain=chain)
         else:
             if isinstance(h, OwedNorm):
                 h = h.materialize()
             if (self.fused_act and h.dtype == torch.bfloat16 and err is not None and self.block == ops.SWIGLU_TILE_BLOCK
                     and ops.pair_gemm_takes(n, 2 * self.spec.intermediate_size, self.spec.hidden_size, fused=True)):
                 # many tokens: the product on pairs of SMs applies the activation to its accumulators
-                act = ops.gemm_pair(h, self.w_gate_up, err, swiglu=True)
+                act = ops.gemm_pair(h, self.w_gate_up, err, swiglu=True, activation=self.spec.activation)
             else:
                 gate_up = linear(h, self.w_gate_up, err=err)
                 act = torch.empty((n, self.spec.intermediate_size), dtype=h.dtype, device=h.device)
