@@ -102,7 +102,7 @@ def close(got, want, dtype, scale=1.0):
 # ======================================================================= mechanisms alone
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("width", [40, 1030])
+@pytest.mark.parametrize("width", [40, 1030, 2048, 4104, 10240])     # the general kernel (1030) and 1, 1, 3, 5 pieces a thread
 def test_branch_norm_layer_scale_residual_and_next_norm(dtype, width):
     from tokamak_b200.csrc import ops
     g = torch.Generator().manual_seed(width)

@@ -56,6 +56,104 @@ __global__ void branch_norm_add_kernel(float* __restrict__ resid, const T* __res
   for (int h = threadIdx.x; h < hidden; h += blockDim.x) o[h] = from_f32<T>(row[h] * rstd * next_w[h]);
 }
 
+// Four neighbouring elements at once (the address is a multiple of four elements).
+template <typename T> __device__ __forceinline__ float4 ld4(const T* p);
+template <> __device__ __forceinline__ float4 ld4<float>(const float* p) { return *reinterpret_cast<const float4*>(p); }
+template <> __device__ __forceinline__ float4 ld4<__nv_bfloat16>(const __nv_bfloat16* p) {
+  const uint2 v = *reinterpret_cast<const uint2*>(p);
+  const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
+  const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
+  return make_float4(lo.x, lo.y, hi.x, hi.y);
+}
+template <typename T> __device__ __forceinline__ void st4(T* p, float4 v);
+template <> __device__ __forceinline__ void st4<float>(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+template <> __device__ __forceinline__ void st4<__nv_bfloat16>(__nv_bfloat16* p, float4 v) {
+  uint2 o;
+  *reinterpret_cast<__nv_bfloat162*>(&o.x) = __floats2bfloat162_rn(v.x, v.y);
+  *reinterpret_cast<__nv_bfloat162*>(&o.y) = __floats2bfloat162_rn(v.z, v.w);
+  *reinterpret_cast<uint2*>(p) = o;
+}
+
+// The same for rows whose length is a multiple of 4: a thread keeps kChunks pieces of four elements
+// in registers through all three steps, so a row is read once and nothing goes through shared memory;
+// the weights, which no kernel writes, are on their way before the kernel in front has finished.
+// With a few rows (decoding) the kernel is three memory latencies long instead of a loop of them.
+template <typename T, int kChunks>
+__global__ void __launch_bounds__(512) branch_norm_add_vec_kernel(float* __restrict__ resid, const T* __restrict__ branch,
+                                           const float* __restrict__ parts, int n_parts, size_t part_stride,
+                                           const float* __restrict__ post_w, const float* __restrict__ layer_scale,
+                                           const float* __restrict__ next_w, T* __restrict__ out,
+                                           const int* __restrict__ rows, int hidden, float eps_b, float eps_n) {
+  __shared__ float scratch[32];
+  pdl_trigger();
+  const float4 ones = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+  float4 w[kChunks], nw[kChunks];
+#pragma unroll
+  for (int c = 0; c < kChunks; ++c) {
+    const int h = (threadIdx.x + c * blockDim.x) * 4;
+    w[c] = ones; nw[c] = ones;
+    if (h < hidden) {
+      if (post_w != nullptr) w[c] = ld4<float>(post_w + h);
+      if (layer_scale != nullptr) {
+        const float4 l = ld4<float>(layer_scale + h);
+        w[c].x *= l.x; w[c].y *= l.y; w[c].z *= l.z; w[c].w *= l.w;
+      }
+      if (out != nullptr) nw[c] = ld4<float>(next_w + h);
+    }
+  }
+  pdl_wait();
+  const int i = blockIdx.x;
+  const int r = rows ? rows[i] : i;
+  float* x = resid + (size_t)r * hidden;
+  float4 b[kChunks], xv[kChunks];
+  float ss = 0.0f;
+#pragma unroll
+  for (int c = 0; c < kChunks; ++c) {
+    const int h = (threadIdx.x + c * blockDim.x) * 4;
+    b[c] = make_float4(0.0f, 0.0f, 0.0f, 0.0f); xv[c] = b[c];
+    if (h < hidden) {
+      xv[c] = ld4<float>(x + h);
+      if (branch != nullptr) {
+        b[c] = ld4<T>(branch + (size_t)r * hidden + h);
+      } else {
+        const float* src = parts + (size_t)r * hidden + h;
+        for (int s = 0; s < n_parts; ++s) {
+          const float4 v = ld4<float>(src + (size_t)s * part_stride);
+          b[c].x += v.x; b[c].y += v.y; b[c].z += v.z; b[c].w += v.w;
+        }
+      }
+      ss += b[c].x * b[c].x + b[c].y * b[c].y + b[c].z * b[c].z + b[c].w * b[c].w;
+    }
+  }
+  ss = block_sum(ss, scratch);
+  const float rstd_b = rsqrtf(ss / (float)hidden + eps_b);
+  float ss2 = 0.0f;
+#pragma unroll
+  for (int c = 0; c < kChunks; ++c) {
+    const int h = (threadIdx.x + c * blockDim.x) * 4;
+    // (branch * rstd) * (post_w * layer_scale): the two weights were multiplied on the way in
+    float4 y = make_float4(b[c].x * rstd_b, b[c].y * rstd_b, b[c].z * rstd_b, b[c].w * rstd_b);
+    if (post_w != nullptr || layer_scale != nullptr) { y.x *= w[c].x; y.y *= w[c].y; y.z *= w[c].z; y.w *= w[c].w; }
+    xv[c].x += y.x; xv[c].y += y.y; xv[c].z += y.z; xv[c].w += y.w;
+    if (h < hidden) {
+      if (rows == nullptr) st4<float>(x + h, xv[c]);
+      ss2 += xv[c].x * xv[c].x + xv[c].y * xv[c].y + xv[c].z * xv[c].z + xv[c].w * xv[c].w;
+    }
+  }
+  if (out == nullptr) return;
+  ss2 = block_sum(ss2, scratch);
+  const float rstd = rsqrtf(ss2 / (float)hidden + eps_n);
+  T* o = out + (size_t)i * hidden;
+#pragma unroll
+  for (int c = 0; c < kChunks; ++c) {
+    const int h = (threadIdx.x + c * blockDim.x) * 4;
+    if (h < hidden) {
+      st4<T>(o + h, make_float4(xv[c].x * rstd * nw[c].x, xv[c].y * rstd * nw[c].y, xv[c].z * rstd * nw[c].z,
+                                xv[c].w * rstd * nw[c].w));
+    }
+  }
+}
+
 }  // namespace tk
 
 TK_API int tk_branch_norm_add(float* resid, const void* branch, const float* parts, int n_parts,
@@ -66,8 +164,24 @@ TK_API int tk_branch_norm_add(float* resid, const void* branch, const float* par
   if (hidden < 1 || hidden > 12288 || (branch == nullptr) == (parts == nullptr) || (out != nullptr && next_w == nullptr)) {
     return (int)cudaErrorInvalidValue;
   }
-  const int threads = hidden >= 1024 ? 256 : 128;
   cudaError_t e = cudaSuccess;
+  if (hidden % 4 == 0) {
+    const int quads = hidden / 4;
+    const int threads = quads >= 512 ? 512 : (quads + 31) / 32 * 32;
+    const int chunks = (quads + threads - 1) / threads;        // at most 6: hidden <= 12288
+#define TK_BRANCH_NORM_VEC(K)                                                                                         \
+    TK_DISPATCH_DTYPE(dtype, T,                                                                                      \
+                      e = tk::launch(tk::branch_norm_add_vec_kernel<T, K>, dim3((unsigned)n_rows), dim3(threads), 0, \
+                                     stream, resid, (const T*)branch, parts, n_parts, (size_t)part_stride, post_w,   \
+                                     layer_scale, next_w, (T*)out, rows, hidden, eps_b, eps_n))
+    if (chunks <= 1) { TK_BRANCH_NORM_VEC(1); }
+    else if (chunks <= 2) { TK_BRANCH_NORM_VEC(2); }
+    else if (chunks <= 4) { TK_BRANCH_NORM_VEC(4); }
+    else { TK_BRANCH_NORM_VEC(8); }
+#undef TK_BRANCH_NORM_VEC
+    return (int)e;
+  }
+  const int threads = hidden >= 1024 ? 256 : 128;
   TK_DISPATCH_DTYPE(dtype, T,
                     e = tk::launch(tk::branch_norm_add_kernel<T>, dim3((unsigned)n_rows), dim3(threads),
                                    (size_t)hidden * sizeof(float), stream, resid, (const T*)branch, parts, n_parts,
