@@ -81,7 +81,8 @@ constexpr int kGlaTile = 4;       // a thread keeps 4 rows (key channels) x 4 co
 constexpr int kGlaMaxWarps = 16;  // working warps of a block
 constexpr int kGlaService = 5;    // serving warps: one copies the inputs in, four add the partial outputs up
 constexpr int kGlaBatch = 8;      // tokens staged in shared memory at a time
-constexpr int kGlaChunk = 16;     // row groups that one lane adds up when the partial outputs are joined
+constexpr int kGlaChunk = 16;     // row groups that one lane adds up when the partial outputs are joined (8 was measured slower)
+constexpr int kGlaChunkPad = 16;  // floats of padding behind a chunk in the buffer of partial outputs
 constexpr int kGlaStages = 4;     // staging buffers: a batch is asked for three batches before it is needed
 constexpr int kGlaMaxKey = 256;   // key_dim: 16 warps of 16 rows at 32 columns a block
 
@@ -134,18 +135,22 @@ __global__ void __launch_bounds__((kGlaMaxWarps + kGlaService) * 32, 1) gla_scan
   const int n_groups = n_warps * kRowGroups;
   const int qka_len = 3 * p.dks;                            // a staged token's q | k | alpha pieces
   const int per_buf = kBatch * (qka_len + kCols);           // staging buffers (stage0 + i * per_buf): the pieces, then the values
-  const int per_out = kBatch * n_groups * kCols;            // partial outputs [kBatch][n_groups][kCols], two of them
+  // partial outputs [kBatch][n_groups][kCols], two of them; every chunk of row groups is followed by 64
+  // bytes of padding, so that the lanes that add up neighbouring chunks read different banks
+  const int out_tok = n_groups * kCols + ((n_groups + kGlaChunk - 1) / kGlaChunk) * kGlaChunkPad;
+  const int per_out = kBatch * out_tok;
   // the first 32 floats: a barrier per staging buffer, and from the 16th on twelve zeros, the inputs of
   // rows beyond key_dim's last piece
   const uint32_t bars = smem_u32(smem);
   const float* zeros = smem + 16;
   float* stage0 = smem + 32;
   float* so = stage0 + kGlaStages * per_buf;
-  for (int i = threadIdx.x; i < 16 + kGlaStages * per_buf; i += blockDim.x) smem[16 + i] = 0.0f;
+  // (the staging buffers need no clearing: what is read of them was copied, or filled with zeros by the copy)
+  if (threadIdx.x < 16) smem[16 + threadIdx.x] = 0.0f;
   if (threadIdx.x == 0) {
     for (int i = 0; i < kGlaStages; ++i) mbar_init(bars + 8 * i, 1);
   }
-  fence_async_shared();       // the zeros and the barriers, before the copy unit writes here
+  fence_async_shared();       // the barriers, before the copy unit reports to them
   __syncthreads();
   volatile __shared__ int no_abort;
   if (threadIdx.x == 0) no_abort = 0;
@@ -197,9 +202,10 @@ __global__ void __launch_bounds__((kGlaMaxWarps + kGlaService) * 32, 1) gla_scan
       }
     };
     // Four columns of a token are added up by 1, 2 or 4 neighbouring lanes: a lane takes sixteen row
-    // groups (64 rows) in their order, then the lanes' sums are joined as (0 + 1) + (2 + 3).  The
-    // grouping follows the rows alone, so the sum is the same whatever the block's shape.
-    const int lanes_per = n_groups <= kGlaChunk ? 1 : n_groups <= 2 * kGlaChunk ? 2 : 4;
+    // groups (64 rows) in their order, then the lanes' sums are joined pairwise, (0 + 1) + (2 + 3).
+    // The grouping follows the rows alone (rows that do not exist add zeros), so the sum is the same
+    // whatever the block's shape.
+    const int lanes_per = n_groups <= kGlaChunk ? 1 : n_groups <= 2 * kGlaChunk ? 2 : n_groups <= 4 * kGlaChunk ? 4 : 8;
     auto reduce = [&](int b) {
       if (sw == 0) return;
       const int t0 = b * kBatch, nb = min(kBatch, n - t0);
@@ -211,7 +217,7 @@ __global__ void __launch_bounds__((kGlaMaxWarps + kGlaService) * 32, 1) gla_scan
         const int item = live ? idx / lanes_per : 0, piece = idx % lanes_per;
         const int tb = item / kColGroups, c = (item % kColGroups) * kGlaTile;
         const int w0 = piece * kGlaChunk, w1 = live ? min(n_groups, w0 + kGlaChunk) : w0;
-        const float4* src = reinterpret_cast<const float4*>(part + tb * n_groups * kCols + c);
+        const float4* src = reinterpret_cast<const float4*>(part + tb * out_tok + piece * kGlaChunkPad + c);
         float4 o = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll 8
         for (int w = w0; w < w1; ++w) {
@@ -268,7 +274,7 @@ __global__ void __launch_bounds__((kGlaMaxWarps + kGlaService) * 32, 1) gla_scan
     const float4* mine = reinterpret_cast<const float4*>(padded ? zeros : buf + group * (3 * kGlaTile));
     const float4* vals = reinterpret_cast<const float4*>(buf + kBatch * qka_len + cg * kGlaTile);
     const int step = padded ? 0 : qka_len / 4;
-    float4* part = reinterpret_cast<float4*>(so + (b & 1) * per_out + group * kCols + cg * kGlaTile);
+    float4* part = reinterpret_cast<float4*>(so + (b & 1) * per_out + group * kCols + (group / kGlaChunk) * kGlaChunkPad + cg * kGlaTile);
     float4 q, k, a, v;
     auto load = [&]() {
       q = mine[0]; k = mine[1]; a = mine[2]; v = vals[0];
@@ -290,7 +296,7 @@ __global__ void __launch_bounds__((kGlaMaxWarps + kGlaService) * 32, 1) gla_scan
         o23 = fma2(q2, s[rr][1], o23);
       }
       *part = make_float4(o01.x, o01.y, o23.x, o23.y);
-      part += n_groups * kCols / 4;
+      part += out_tok / 4;
     };
     load();
     if (nb == kBatch) {       // a full batch: a loop of known length
@@ -374,7 +380,8 @@ static cudaError_t gla_scan_launch(const tk::GlaScanParams& p, int n_reqs, cudaS
   const int n_groups = n_warps * kRowGroups;
   const int col_tiles = (p.value_dim + kCols - 1) / kCols;
   if (n_warps > tk::kGlaMaxWarps || col_tiles > 65535) return cudaErrorInvalidValue;
-  const size_t smem = sizeof(float) * (32 + (size_t)tk::kGlaStages * kBatch * (3 * p.dks + kCols) + (size_t)2 * kBatch * n_groups * kCols);
+  const size_t out_tok = (size_t)n_groups * kCols + (size_t)((n_groups + tk::kGlaChunk - 1) / tk::kGlaChunk) * tk::kGlaChunkPad;
+  const size_t smem = sizeof(float) * (32 + (size_t)tk::kGlaStages * kBatch * (3 * p.dks + kCols) + 2 * kBatch * out_tok);
   cudaError_t e = cudaSuccess;
   if (smem > 48 * 1024) {
     e = cudaFuncSetAttribute(tk::gla_scan_kernel<kCols>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
