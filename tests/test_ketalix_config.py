@@ -116,3 +116,20 @@ def test_plain_prefix_property_and_state_carry():
         decay = a[t + 1:].prod(dim=0)
         S += decay[:, :, None] * k[t][:, :, None] * v[t][:, None, :]
     assert torch.allclose(S, s, atol=1e-10)
+
+
+def test_random_folder_from_the_command_line(tmp_path, capsys):
+    """The writer of seeded random folders takes the design's config.json like any other."""
+    import json
+
+    from tokamak_b200.cli import main
+    from tokamak_b200.weights.loader import checkpoint_shapes
+
+    cfg = tmp_path / "cfg.json"
+    cfg.write_text(json.dumps(kc.KX_B))
+    out = tmp_path / "model"
+    assert main(["--write-random", str(out), "--config", str(cfg), "--seed", "4", "--weights-dtype", "float32"]) == 0
+    assert "wrote" in capsys.readouterr().out
+    shapes = checkpoint_shapes(out)
+    assert shapes["embed"] == (kc.KX_B["vocab"], kc.KX_B["width"]) and shapes["l0.mix.a1"][1] == kc.KX_B["width"]
+    assert "l2.mlp.gate" not in shapes and "l1.mlp.gate" in shapes          # the third layer has no feed-forward

@@ -550,3 +550,16 @@ def test_trace_run_program_on_this_design(tmp_path):
     vocab = kc.ALL[tag][0]["vocab"]
     results = {s: np.fromfile(out / f"{s}.f32", dtype="<f4").reshape(-1, vocab) for s in rows}
     check_rows(results, rows, reqs, folder, dtype, "trace_run")
+
+
+def test_generation_from_the_command_line(capsys):
+    """The command line on a folder of this design: greedy tokens for a seeded random prompt, the same
+    at every call."""
+    from tokamak_b200.cli import main
+    folder = folder_of("KA", "float32")
+    argv = ["--model", str(folder), "--dtype", "float32", "--prompt-len", "21", "--temperature", "0",
+            "--max-new-tokens", "9", "--ignore-eos", "--block-size", "16", "--max-seq-len", "64", "--kv-pool-tokens", "256"]
+    assert main(argv) == 0
+    first = capsys.readouterr().out
+    assert main(argv) == 0
+    assert capsys.readouterr().out == first and first.strip()
