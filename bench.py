@@ -908,7 +908,14 @@ def ketalix_kernels(s: dict, tokens: int, batch: int, ctx: int, peaks: dict) -> 
     row("gelu gate", "silu gate (the unfused kernel)",
         _time_us(lambda: ops.swiglu(gu, act, block=ops.SWIGLU_TILE_BLOCK, activation="gelu_tanh")),
         _time_us(lambda: ops.swiglu(gu, act, block=ops.SWIGLU_TILE_BLOCK)), nbytes=3 * tokens * ff * 2,
-        note="Qwen3 applies silu in its products' epilogues; the gelu gate runs as a kernel of its own")
+        note="the kernel of its own, for float32 and for sizes that are no multiple of 64: both models' "
+             "bfloat16 products apply the gate in their epilogues (next row)")
+    wgu = bf(2 * ff, width) * (width ** -0.5)
+    xin = bf(tokens, width)
+    if ops.pair_gemm_takes(tokens, 2 * ff, width, fused=True):
+        row("gate/up product with the gelu gate in its epilogue", "the same with the silu gate",
+            _time_us(lambda: ops.gemm_pair(xin, wgu, err, swiglu=True, activation="gelu_tanh")),
+            _time_us(lambda: ops.gemm_pair(xin, wgu, err, swiglu=True)), flops=2.0 * tokens * 2 * ff * width)
     # ---- gated linear attention
     gh, gk, gv, rank = width // 256, 128, 256, 16
     rowlen = 2 * gh * gk + 2 * gh * gv + rank

@@ -160,7 +160,7 @@ def _paged(k, v, page, seed, dtype, extra_pages=3):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("d,dv,rot", [(16, 24, 8), (32, 32, 32), (8, 40, 0), (70, 6, 34)])
+@pytest.mark.parametrize("d,dv,rot", [(16, 24, 8), (32, 32, 32), (8, 40, 0), (70, 6, 34), (128, 128, 64), (64, 256, 64), (256, 8, 256)])
 def test_pair_rotation_unit_norm_value_blend_and_page_write(dtype, d, dv, rot):
     from tokamak_b200.csrc import ops
     H, G, T, page = 4, 2, 37, 8

@@ -145,6 +145,125 @@ __global__ void qkv_pairs_kernel(QkvPairsParams p) {
   }
 }
 
+// Eight neighbouring elements (the address is a multiple of eight elements).
+template <typename T> __device__ __forceinline__ void ld8(const T* p, float (&v)[8]);
+template <> __device__ __forceinline__ void ld8<float>(const float* p, float (&v)[8]) {
+  const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+template <> __device__ __forceinline__ void ld8<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[8]) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[i]));
+    v[2 * i] = f.x; v[2 * i + 1] = f.y;
+  }
+}
+template <typename T> __device__ __forceinline__ void st8(T* p, const float (&v)[8]);
+template <> __device__ __forceinline__ void st8<float>(float* p, const float (&v)[8]) {
+  reinterpret_cast<float4*>(p)[0] = make_float4(v[0], v[1], v[2], v[3]);
+  reinterpret_cast<float4*>(p)[1] = make_float4(v[4], v[5], v[6], v[7]);
+}
+template <> __device__ __forceinline__ void st8<__nv_bfloat16>(__nv_bfloat16* p, const float (&v)[8]) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    w[i] = *reinterpret_cast<const uint32_t*>(&h);
+  }
+  *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// The same for head sizes and a rotated part that are multiples of 8 and an input in the activation
+// type: a lane takes eight neighbouring elements (four pairs), so every access is 16 or 32 bytes.
+// One warp per (token, head); heads of up to 256 elements.
+template <typename T>
+__global__ void qkv_pairs_vec_kernel(QkvPairsParams p) {
+  pdl_trigger();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int heads_total = p.n_q_heads + 2 * p.n_kv_heads;
+  const int t = blockIdx.x;
+  const int h = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (h >= heads_total) return;
+  int kind, head;     // 0 = q, 1 = k, 2 = v
+  if (h < p.n_q_heads) { kind = 0; head = h; }
+  else if (h < p.n_q_heads + p.n_kv_heads) { kind = 1; head = h - p.n_q_heads; }
+  else { kind = 2; head = h - p.n_q_heads - p.n_kv_heads; }
+  const int d = (kind == 2) ? p.v_dim : p.k_dim;
+  const T* src = (const T*)p.qkv + (size_t)t * p.row_stride +
+      (kind == 0 ? (size_t)head * p.k_dim
+                 : kind == 1 ? (size_t)(p.n_q_heads + head) * p.k_dim
+                             : (size_t)(p.n_q_heads + p.n_kv_heads) * p.k_dim + (size_t)head * p.v_dim);
+  const int e = 8 * lane;
+  const bool mine = e < d;
+  float x[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+  if (mine) ld8<T>(src + e, x);       // asked for before the page is looked up
+
+  T* dst;
+  int zero_rows = 0;
+  if (kind == 0) {
+    dst = (T*)p.q_out + ((size_t)t * p.n_q_heads + head) * d;
+  } else {
+    const int pos = p.positions[t];
+    const int r = p.tok_req[t];
+    if (pos < 0) { if (lane == 0) set_error(p.err, kErrPosition, t, pos, 0); return; }
+    if (r < 0 || r >= p.n_reqs) { if (lane == 0) set_error(p.err, kErrRequest, t, r, p.n_reqs); return; }
+    const int pidx = pos / p.page_size;
+    const int slot = pos - pidx * p.page_size;
+    const int page = (pidx < p.max_pages) ? p.block_table[(size_t)p.req_slot[r] * p.max_pages + pidx] : -1;
+    if (page < 0 || page >= p.num_pages) { if (lane == 0) set_error(p.err, kErrPage, t, pidx, page); return; }
+    dst = (T*)(kind == 1 ? p.k_cache : p.v_cache) + (((size_t)page * p.n_kv_heads + head) * p.page_size + slot) * d;
+    if (p.req_kv_len != nullptr) {      // see the general kernel: the rest of a page begun in this step is cleared
+      const int kv_len = p.req_kv_len[r], q_len = p.req_q_len[r];
+      if (pos == kv_len - 1 && pos - slot >= kv_len - q_len) zero_rows = p.page_size - 1 - slot;
+    }
+  }
+  if (mine) {
+    const float zeros[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+    for (int z = 1; z <= zero_rows; ++z) st8<T>(dst + (size_t)z * d + e, zeros);
+  }
+
+  if (kind == 2) {
+    if (!mine) return;
+    const size_t vo = ((size_t)t * p.n_kv_heads + head) * d + e;
+    if (p.v_first_out != nullptr) st8<float>(p.v_first_out + vo, x);
+    if (p.v_first_in != nullptr) {
+      const float lam = *p.v_lambda;
+      float f[8];
+      ld8<float>(p.v_first_in + vo, f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) x[i] = (1.0f - lam) * x[i] + lam * f[i];
+    }
+    st8<T>(dst + e, x);
+    return;
+  }
+
+  float ss = 0.0f;
+  if (mine) {
+    if (p.rope_table != nullptr && e < p.rotary_dim) {
+      float cs[8];      // (cos, sin) of the lane's four pairs
+      ld8<float>(reinterpret_cast<const float*>(p.rope_table + (size_t)t * (p.rotary_dim >> 1) + (e >> 1)), cs);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float u = x[2 * i], w = x[2 * i + 1];
+        x[2 * i] = u * cs[2 * i] - w * cs[2 * i + 1];
+        x[2 * i + 1] = w * cs[2 * i] + u * cs[2 * i + 1];
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss += x[i] * x[i];
+  }
+  if (p.unit_norm) {
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss / (float)d + p.eps);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) x[i] *= rstd;
+  }
+  if (mine) st8<T>(dst + e, x);
+}
+
 }  // namespace tk
 
 TK_API int tk_qkv_pairs(const void* qkv, const float* qkv_parts, int n_parts, void* q_out, void* k_cache,
@@ -174,6 +293,12 @@ TK_API int tk_qkv_pairs(const void* qkv, const float* qkv_parts, int n_parts, vo
   const int groups = (heads_total + warps - 1) / warps;
   if (groups > 65535) return (int)cudaErrorInvalidValue;
   cudaError_t e = cudaSuccess;
+  if (qkv_parts == nullptr && k_dim % 8 == 0 && v_dim % 8 == 0 && rotary_dim % 8 == 0 && v_dim <= 256 && row_stride % 8 == 0) {
+    TK_DISPATCH_DTYPE(dtype, T,
+                      e = tk::launch(tk::qkv_pairs_vec_kernel<T>, dim3((unsigned)n_tokens, (unsigned)groups),
+                                     dim3(warps * 32), 0, stream, p));
+    return (int)e;
+  }
   TK_DISPATCH_DTYPE(dtype, T,
                     e = tk::launch(tk::qkv_pairs_kernel<T>, dim3((unsigned)n_tokens, (unsigned)groups),
                                    dim3(warps * 32), 0, stream, p));
