@@ -16,6 +16,8 @@
 //
 // The inputs are columns of one stacked projection output [tokens, row_stride] (in the
 // activation type, or float32 partial sums [parts, tokens, row_stride] of a split-K product).
+// Three kernels: gla_prepare_kernel turns them into the recurrence's float32 inputs (scaled q, k,
+// decays, v) once per step, gla_scan_kernel is the recurrence, gla_out_kernel the output stage.
 #include "common.cuh"
 #include "mma_utils.cuh"
 #include "tcgen05_utils.cuh"
