@@ -299,7 +299,7 @@ def test_tiled_attention_kernels_in_prompts_and_in_decoding(d, H, G, page, windo
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("H,dk,dv,rank", [(2, 12, 20, 5), (1, 40, 40, 8), (3, 64, 80, 4), (2, 130, 33, 1)])
+@pytest.mark.parametrize("H,dk,dv,rank", [(2, 12, 20, 5), (1, 40, 40, 8), (3, 64, 80, 4), (2, 130, 33, 1), (2, 32, 24, 16)])
 def test_gla_decay_recurrence_state_and_output_stage(dtype, H, dk, dv, rank):
     from tokamak_b200.csrc import ops
     g = torch.Generator().manual_seed(dk)

@@ -40,6 +40,22 @@ __device__ __forceinline__ float gla_ld(const GlaInput& in, size_t off) {
   return acc;
 }
 
+// Eight neighbouring elements as float32 (the address is a multiple of eight elements).
+template <typename T> __device__ __forceinline__ void gla_ld8(const T* p, float (&v)[8]);
+template <> __device__ __forceinline__ void gla_ld8<float>(const float* p, float (&v)[8]) {
+  const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+template <> __device__ __forceinline__ void gla_ld8<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[8]) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[i]));
+    v[2 * i] = f.x; v[2 * i + 1] = f.y;
+  }
+}
+
 // What the recurrence reads, float32 whatever the engine's dtype, head by head so that a head's
 // tokens lie one after the other and a batch of them is one bulk copy:
 //   [heads][tokens][dks / 4 pieces of  q * q_scale [4] | k [4] | alpha [4]  (four key channels each)]
@@ -72,7 +88,21 @@ __global__ void gla_prepare_kernel(GlaInput in, int q_off, int k_off, int v_off,
   if (e >= dk) { piece[0] = 0.0f; piece[4] = 0.0f; piece[8] = 0.0f; return; }
   const int ch = h * dk + e;
   float z = 0.0f;
-  for (int j = 0; j < rank; ++j) z += gla_ld<T>(in, row + a_off + j) * to_f32<T>(w2[(size_t)ch * rank + j]);
+  if (in.parts == nullptr && (rank & 7) == 0 && ((row + a_off) & 7) == 0) {
+    // the usual case: eight factors a load (the dot product of `rank` steps is what this kernel waits for);
+    // the sum runs in the order of the plain loop
+    const T* arow = (const T*)in.x + row + a_off;
+    const T* wrow = w2 + (size_t)ch * rank;
+    for (int j = 0; j < rank; j += 8) {
+      float a8[8], w8[8];
+      gla_ld8<T>(arow + j, a8);
+      gla_ld8<T>(wrow + j, w8);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) z += a8[i] * w8[i];
+    }
+  } else {
+    for (int j = 0; j < rank; ++j) z += gla_ld<T>(in, row + a_off + j) * to_f32<T>(w2[(size_t)ch * rank + j]);
+  }
   if (bias != nullptr) z += bias[ch];
   piece[0] = gla_ld<T>(in, row + q_off + ch) * q_scale;
   piece[4] = gla_ld<T>(in, row + k_off + ch);
