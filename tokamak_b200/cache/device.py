@@ -93,7 +93,14 @@ class DeviceCache:
         self._pool_groups: list[KVGroup] = []      # the group of every entry of _pools
         for gi, g in enumerate(manager.kv_groups):
             shape = (len(g.cache_keys), 2, g.num_pages, g.need.n_kv_heads, g.page_size)
-            if g.need.value_dim == g.need.head_dim:
+            if g.need.values_in_keys:
+                if g.need.value_dim > g.need.head_dim:
+                    raise ValueError("values that are part of their keys cannot be longer than the keys")
+                k_pool = torch.zeros((shape[0], 1) + shape[2:] + (g.need.head_dim,), dtype=dtype, device=device)
+                k_of = lambda i, t=k_pool: t[i, 0]
+                v_of = lambda i, t=k_pool, dv=g.need.value_dim: t[i, 0][..., :dv]
+                pools = [k_pool]
+            elif g.need.value_dim == g.need.head_dim:
                 pool = torch.zeros(shape + (g.need.head_dim,), dtype=dtype, device=device)
                 k_of, v_of = (lambda i, pool=pool: pool[i, 0]), (lambda i, pool=pool: pool[i, 1])
                 pools = [pool]
@@ -125,7 +132,7 @@ class DeviceCache:
         total = 0
         elem = torch.empty((), dtype=self.dtype).element_size()
         for g in self.manager.kv_groups:
-            total += len(g.cache_keys) * g.need.n_kv_heads * (g.need.head_dim + g.need.value_dim) * elem
+            total += len(g.cache_keys) * g.need.n_kv_heads * g.need.stored_dim * elem
         return total
 
     # ---- the engine's records ----------------------------------------------------------------

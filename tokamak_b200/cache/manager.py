@@ -46,18 +46,26 @@ class KVPagesNeed:
 
     ``window`` is the number of most recent positions a query sees (itself
     included), or ``None`` when it sees all of them.  ``v_head_dim`` is the size of a value
-    head where it differs from the key head's (``None``: the same).
+    head where it differs from the key head's (``None``: the same).  ``values_in_keys`` says that a
+    value is the leading ``v_head_dim`` elements of its key row (a latent cache): no value pages are
+    kept, and the view's values are a view of the key pages.
     """
 
     n_kv_heads: int
     head_dim: int
     window: int | None = None
     v_head_dim: int | None = None
+    values_in_keys: bool = False
     kind: str = "kv_pages"
 
     @property
     def value_dim(self) -> int:
         return self.head_dim if self.v_head_dim is None else self.v_head_dim
+
+    @property
+    def stored_dim(self) -> int:
+        """Elements that one position of one head occupies in the pools."""
+        return self.head_dim if self.values_in_keys else self.head_dim + self.value_dim
 
 
 @dataclass(frozen=True)

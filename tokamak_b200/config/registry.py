@@ -139,3 +139,6 @@ def _load_builtin() -> None:
         from ..models import ketalix
         register_architecture(Architecture(ketalix.ARCHITECTURE, ketalix.parse_config, ketalix.model_spec,
                                            reads_tensor_shapes=True))
+    if "Logivik" not in _ARCHITECTURES:
+        from ..models import logivik
+        register_architecture(Architecture(logivik.ARCHITECTURE, logivik.parse_config, logivik.model_spec))

@@ -1,5 +1,5 @@
 // Paged attention, general form: any mix of prompt portions and single decoded
-// tokens, any head_dim up to 256, any group size, float32 or bfloat16 pages.
+// tokens, any head_dim up to 1024, any group size, float32 or bfloat16 pages.
 //
 // One thread block per (token, query head).  The query at absolute position p
 // sees keys [max(0, p - window + 1), p] of its own request (window <= 0: all),
@@ -13,19 +13,20 @@
 // Options that other designs use: values of another size than keys (v_dim), a soft cap on the
 // scaled scores (score <- cap * tanh(score / cap), cap <= 0: none), and a sink per query head:
 // a learned number whose exponential joins the softmax denominator once, with no key and no
-// value, neither scaled nor capped.
+// value, neither scaled nor capped.  Queries may be float32 over bfloat16 pages and are addressed by
+// a token and a head stride; key and value rows have strides of their own, so that values which are the
+// leading elements of the key rows (a latent cache) are read from the key pages.
 #include "common.cuh"
 
 namespace tk {
 
-constexpr int kPlainMaxPerLane = 8;  // head_dim <= 256
 constexpr int kPlainWarps = 4;
 
 struct AttnParams {
-  const void* q;            // [n_tokens, n_q_heads, head_dim]
+  const void* q;            // element (t, h, e) at t * q_tok_stride + h * q_head_stride + e
   void* out;                // [n_tokens, n_q_heads, v_dim]
-  const void* k_cache;      // [num_pages, n_kv_heads, page_size, head_dim]
-  const void* v_cache;      // [num_pages, n_kv_heads, page_size, v_dim]
+  const void* k_cache;      // [num_pages, n_kv_heads, page_size, k_stride]: a row's first head_dim elements
+  const void* v_cache;      // [num_pages, n_kv_heads, page_size, v_stride]: a row's first v_dim elements
   const float* sinks;       // [n_q_heads] or null
   const int* positions;     // [n_tokens]
   const int* tok_req;       // [n_tokens]
@@ -35,11 +36,15 @@ struct AttnParams {
   int* err;
   int n_tokens, n_reqs, n_q_heads, n_kv_heads, head_dim;
   int page_size, max_pages, num_pages, window, v_dim;
+  long long q_tok_stride, q_head_stride;
+  int k_stride, v_stride;
   float scale, softcap;
 };
 
-template <typename T>
+// TQ: element type of the queries, T: of pages and output; kPerLane: elements of a head per lane.
+template <typename TQ, typename T, int kPerLane>
 __global__ void attention_plain_kernel(AttnParams p) {
+  constexpr int kPlainMaxPerLane = kPerLane;
   pdl_trigger();
   pdl_wait();
   __shared__ float s_m[kPlainWarps];
@@ -63,13 +68,13 @@ __global__ void attention_plain_kernel(AttnParams p) {
   const int* table = p.block_table + (size_t)p.req_slot[r] * p.max_pages;
   const int lo = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
 
-  const T* qrow = (const T*)p.q + ((size_t)t * p.n_q_heads + hq) * d;
+  const TQ* qrow = (const TQ*)p.q + (size_t)t * p.q_tok_stride + (size_t)hq * p.q_head_stride;
   float qreg[kPlainMaxPerLane];
   float acc[kPlainMaxPerLane];
 #pragma unroll
   for (int i = 0; i < kPlainMaxPerLane; ++i) {
     const int e = i * 32 + lane;
-    qreg[i] = (e < d) ? to_f32<T>(qrow[e]) * p.scale : 0.0f;
+    qreg[i] = (e < d) ? to_f32<TQ>(qrow[e]) * p.scale : 0.0f;
     acc[i] = 0.0f;
   }
   float m = -INFINITY, l = 0.0f;
@@ -85,8 +90,8 @@ __global__ void attention_plain_kernel(AttnParams p) {
       break;
     }
     const size_t row = ((size_t)page * p.n_kv_heads + hkv) * p.page_size + (j % p.page_size);
-    const T* krow = (const T*)p.k_cache + row * d;
-    const T* vrow = (const T*)p.v_cache + row * dv;
+    const T* krow = (const T*)p.k_cache + row * p.k_stride;
+    const T* vrow = (const T*)p.v_cache + row * p.v_stride;
     float dot = 0.0f;
 #pragma unroll
     for (int i = 0; i < kPlainMaxPerLane; ++i) {
@@ -145,11 +150,13 @@ TK_API int tk_attention_plain(const void* q, void* out, const void* k_cache, con
                               const int* block_table, const int* items, int* err, int n_tokens, int n_reqs,
                               int n_q_heads, int n_kv_heads, int head_dim, int page_size,
                               int max_pages, int num_pages, int window, float scale, int dtype,
-                              int v_dim, float softcap, const float* sinks, cudaStream_t stream) {
+                              int v_dim, float softcap, const float* sinks, int q_dtype, long long q_tok_stride,
+                              long long q_head_stride, int k_stride, int v_stride, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (v_dim <= 0) v_dim = head_dim;
-  if (head_dim < 1 || head_dim > tk::kPlainMaxPerLane * 32 || v_dim > tk::kPlainMaxPerLane * 32 || n_kv_heads < 1 ||
-      n_q_heads % n_kv_heads != 0 || n_q_heads > 65535) {
+  const int widest = head_dim > v_dim ? head_dim : v_dim;
+  if (head_dim < 1 || widest > 1024 || n_kv_heads < 1 || n_q_heads % n_kv_heads != 0 || n_q_heads > 65535 ||
+      k_stride < head_dim || v_stride < v_dim || (q_dtype != dtype && q_dtype != tk::kF32)) {
     return (int)cudaErrorInvalidValue;
   }
   tk::AttnParams p;
@@ -159,9 +166,25 @@ TK_API int tk_attention_plain(const void* q, void* out, const void* k_cache, con
   p.n_kv_heads = n_kv_heads; p.head_dim = head_dim; p.page_size = page_size;
   p.max_pages = max_pages; p.num_pages = num_pages; p.window = window; p.scale = scale;
   p.v_dim = v_dim; p.softcap = softcap; p.sinks = sinks;
+  p.q_tok_stride = q_tok_stride; p.q_head_stride = q_head_stride; p.k_stride = k_stride; p.v_stride = v_stride;
   dim3 grid(n_tokens, n_q_heads);
   cudaError_t e = cudaSuccess;
-  TK_DISPATCH_DTYPE(dtype, T,
-                    e = tk::launch(tk::attention_plain_kernel<T>, grid, dim3(tk::kPlainWarps * 32), 0, stream, p));
+#define TK_PLAIN_LAUNCH(TQ, K)                                                                                   \
+  TK_DISPATCH_DTYPE(dtype, T, e = tk::launch(tk::attention_plain_kernel<TQ, T, K>, grid, dim3(tk::kPlainWarps * 32), \
+                                             0, stream, p))
+#define TK_PLAIN_SIZES(TQ)                                   \
+  do {                                                       \
+    if (widest <= 128) { TK_PLAIN_LAUNCH(TQ, 4); }           \
+    else if (widest <= 256) { TK_PLAIN_LAUNCH(TQ, 8); }      \
+    else if (widest <= 640) { TK_PLAIN_LAUNCH(TQ, 20); }     \
+    else { TK_PLAIN_LAUNCH(TQ, 32); }                        \
+  } while (0)
+  if (q_dtype == dtype) {
+    if (dtype == tk::kF32) { TK_PLAIN_SIZES(float); } else { TK_PLAIN_SIZES(__nv_bfloat16); }
+  } else {
+    TK_PLAIN_SIZES(float);
+  }
+#undef TK_PLAIN_SIZES
+#undef TK_PLAIN_LAUNCH
   return (int)e;
 }

@@ -3,6 +3,7 @@
 //   y = branch * rsqrt(mean(branch^2) + eps_b) * post_w (* layer_scale)
 //   x = resid + y                      (written back to resid unless `rows` selects rows)
 //   out = x * rsqrt(mean(x^2) + eps_n) * next_w          (when a norm follows)
+//   out = x                                              (next_w null: the next sublayer reads the stream itself)
 //
 // in one pass: the norm after a sublayer, the per-channel layer scale, the 32-bit residual sum
 // and the norm in front of the next sublayer.  Statistics, sums and the residual stream are
@@ -50,9 +51,13 @@ __global__ void branch_norm_add_kernel(float* __restrict__ resid, const T* __res
     ss2 += v * v;
   }
   if (out == nullptr) return;
+  T* o = out + (size_t)i * hidden;
+  if (next_w == nullptr) {
+    for (int h = threadIdx.x; h < hidden; h += blockDim.x) o[h] = from_f32<T>(row[h]);
+    return;
+  }
   ss2 = block_sum(ss2, scratch);
   const float rstd = rsqrtf(ss2 / (float)hidden + eps_n);
-  T* o = out + (size_t)i * hidden;
   for (int h = threadIdx.x; h < hidden; h += blockDim.x) o[h] = from_f32<T>(row[h] * rstd * next_w[h]);
 }
 
@@ -98,7 +103,7 @@ __global__ void __launch_bounds__(512) branch_norm_add_vec_kernel(float* __restr
         const float4 l = ld4<float>(layer_scale + h);
         w[c].x *= l.x; w[c].y *= l.y; w[c].z *= l.z; w[c].w *= l.w;
       }
-      if (out != nullptr) nw[c] = ld4<float>(next_w + h);
+      if (out != nullptr && next_w != nullptr) nw[c] = ld4<float>(next_w + h);
     }
   }
   pdl_wait();
@@ -141,8 +146,8 @@ __global__ void __launch_bounds__(512) branch_norm_add_vec_kernel(float* __restr
     }
   }
   if (out == nullptr) return;
-  ss2 = block_sum(ss2, scratch);
-  const float rstd = rsqrtf(ss2 / (float)hidden + eps_n);
+  // without a norm in front of the next sublayer the row goes out as it is (every thread takes the same branch)
+  const float rstd = next_w != nullptr ? rsqrtf(block_sum(ss2, scratch) / (float)hidden + eps_n) : 1.0f;
   T* o = out + (size_t)i * hidden;
 #pragma unroll
   for (int c = 0; c < kChunks; ++c) {
@@ -161,7 +166,7 @@ TK_API int tk_branch_norm_add(float* resid, const void* branch, const float* par
                               const float* next_w, void* out, const int* rows, int n_rows, int hidden,
                               float eps_b, float eps_n, int dtype, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
-  if (hidden < 1 || hidden > 12288 || (branch == nullptr) == (parts == nullptr) || (out != nullptr && next_w == nullptr)) {
+  if (hidden < 1 || hidden > 12288 || (branch == nullptr) == (parts == nullptr)) {
     return (int)cudaErrorInvalidValue;
   }
   cudaError_t e = cudaSuccess;

@@ -1,0 +1,359 @@
+// Gated delta rule: a matrix-valued recurrent state per (request, head) that is decayed by one
+// number per token and head and corrected, under the token's key, towards the token's value:
+//
+//   S <- g S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q          S: [key_dim, value_dim]
+//
+// and what feeds it.  q, k and v are columns of one stacked projection that pass a short causal
+// convolution over time per channel (taps [channels, K], the last tap weighs the current token) and
+// silu; q and k heads are then scaled to unit length, x / sqrt(sum(x^2) + eps), q also by q_scale;
+// value head h reads q/k head h / (heads / kv_heads).  Per token and head, from two more columns,
+//   beta = sigmoid(b),    g = exp(-exp(A_log[h]) * softplus(a + dt_bias[h])).
+//
+// A request's record in the state pool is  [ S: heads * key_dim * value_dim | tail: (K - 1) * channels ],
+// float32: the state and the last K - 1 inputs of the convolution (oldest first; zeros for a request
+// that has just begun).  Three kernels: delta_prepare_kernel (convolution, silu, unit norm, beta, g;
+// float32 outputs), delta_tail_kernel (moves the convolution's tail on), delta_scan_kernel (the
+// recurrence).  Everything but the stacked projection itself is float32 in every engine dtype.  A
+// request's tokens are walked in order by the blocks that own its state with the same operations
+// in the same order wherever a step begins, so a position's result does not depend on how the
+// prompt was cut or on what else is in the batch.
+#include "common.cuh"
+#include "stacked_input.cuh"
+
+namespace tk {
+
+constexpr int kDeltaMaxTaps = 8;
+constexpr int kDeltaPrepWarps = 4;
+
+struct DeltaPrepareParams {
+  StackedInput in;
+  int q_off, k_off, v_off, b_off, a_off;   // first columns of the pieces of a row
+  const float* taps;          // [channels, n_taps]: q channels, k channels, v channels
+  const float* a_log;         // [heads]
+  const float* dt_bias;       // [heads]
+  const float* state;         // the pool of records
+  long long rec_stride;       // floats per record
+  long long tail_off;         // where the tail starts inside a record
+  const int* tok_req;
+  const int* req_q_start;
+  const int* req_slot;
+  float* q_out;               // [n_tokens, kv_heads, key_dim]
+  float* k_out;               // [n_tokens, kv_heads, key_dim]
+  float* v_out;               // [n_tokens, heads, value_dim]
+  float* beta_out;            // [n_tokens, heads]
+  float* g_out;               // [n_tokens, heads]
+  int* err;
+  int n_tokens, n_reqs, n_slots, heads, kv_heads, dk, dv, n_taps;
+  float unit_eps, q_scale;
+};
+
+// One warp per (token, head unit); the units of a token are its q heads, its k heads, its v heads.
+template <typename T>
+__global__ void delta_prepare_kernel(DeltaPrepareParams p) {
+  pdl_trigger();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x;
+  const int unit = blockIdx.y * kDeltaPrepWarps + (threadIdx.x >> 5);
+  const int units = 2 * p.kv_heads + p.heads;
+  if (unit >= units) return;
+  int kind, head;      // 0 = q, 1 = k, 2 = v
+  if (unit < p.kv_heads) { kind = 0; head = unit; }
+  else if (unit < 2 * p.kv_heads) { kind = 1; head = unit - p.kv_heads; }
+  else { kind = 2; head = unit - 2 * p.kv_heads; }
+  const int d = kind == 2 ? p.dv : p.dk;
+  const int hk = p.kv_heads * p.dk;
+  const int chan0 = kind == 0 ? head * p.dk : kind == 1 ? hk + head * p.dk : 2 * hk + head * p.dv;
+  const int col0 = kind == 0 ? p.q_off + head * p.dk : kind == 1 ? p.k_off + head * p.dk : p.v_off + head * p.dv;
+  const int channels = 2 * hk + p.heads * p.dv;
+  const int r = p.tok_req[t];
+  if (r < 0 || r >= p.n_reqs) { if (lane == 0) set_error(p.err, kErrRequest, t, r, p.n_reqs); return; }
+  const int slot = p.req_slot[r];
+  if (slot < 0 || slot >= p.n_slots) { if (lane == 0) set_error(p.err, kErrRequest, t, slot, p.n_slots); return; }
+  const int i = t - p.req_q_start[r];          // place of the token among its request's tokens of this step
+  const float* tail = p.state + (size_t)slot * p.rec_stride + p.tail_off;
+  const int K = p.n_taps;
+
+  float* dst = kind == 0 ? p.q_out + ((size_t)t * p.kv_heads + head) * p.dk
+             : kind == 1 ? p.k_out + ((size_t)t * p.kv_heads + head) * p.dk
+                         : p.v_out + ((size_t)t * p.heads + head) * p.dv;
+  float ss = 0.0f;
+  for (int e = lane; e < d; e += 32) {
+    const float* w = p.taps + (size_t)(chan0 + e) * K;
+    float acc = 0.0f;
+    for (int j = 0; j < K; ++j) {
+      const int s = i - (K - 1) + j;           // the input's place in this step; negative: before it
+      const float x = s >= 0 ? stacked_ld<T>(p.in, (size_t)(t - i + s) * p.in.row_stride + col0 + e)
+                             : tail[(size_t)(K - 1 + s) * channels + chan0 + e];
+      acc += w[j] * x;
+    }
+    const float y = acc / (1.0f + expf(-acc));
+    dst[e] = y;
+    ss += y * y;
+  }
+  if (kind != 2) {
+    ss = warp_sum(ss);
+    const float f = rsqrtf(ss + p.unit_eps) * (kind == 0 ? p.q_scale : 1.0f);
+    __syncwarp();
+    for (int e = lane; e < d; e += 32) dst[e] *= f;     // each lane rescales what it wrote itself
+  } else if (lane == 0) {
+    const size_t row = (size_t)t * p.in.row_stride;
+    const float b = stacked_ld<T>(p.in, row + p.b_off + head);
+    const float a = stacked_ld<T>(p.in, row + p.a_off + head) + p.dt_bias[head];
+    const float sp = a > 20.0f ? a : log1pf(expf(a));
+    p.beta_out[(size_t)t * p.heads + head] = 1.0f / (1.0f + expf(-b));
+    p.g_out[(size_t)t * p.heads + head] = expf(-expf(p.a_log[head]) * sp);
+  }
+}
+
+// The record's tail after the step: the last K - 1 inputs of every channel.  One thread per
+// (request, channel) reads what it needs of the old tail before it writes.
+template <typename T>
+__global__ void delta_tail_kernel(StackedInput in, int q_off, int k_off, int v_off, float* __restrict__ state,
+                                  long long rec_stride, long long tail_off, const int* __restrict__ req_q_start,
+                                  const int* __restrict__ req_q_len, const int* __restrict__ req_slot, int n_slots,
+                                  int hk, int hv, int n_taps) {
+  pdl_trigger();
+  pdl_wait();
+  const int channels = 2 * hk + hv;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int r = blockIdx.y;
+  if (c >= channels) return;
+  const int slot = req_slot[r];
+  if (slot < 0 || slot >= n_slots) return;            // reported by the kernel before
+  const int col = c < hk ? q_off + c : c < 2 * hk ? k_off + (c - hk) : v_off + (c - 2 * hk);
+  const int n = req_q_len[r], t0 = req_q_start[r];
+  float* tail = state + (size_t)slot * rec_stride + tail_off;
+  const int K = n_taps;
+  float keep[kDeltaMaxTaps];
+#pragma unroll
+  for (int j = 0; j < kDeltaMaxTaps - 1; ++j) {
+    if (j < K - 1) {
+      const int s = n - (K - 1) + j;
+      keep[j] = s >= 0 ? stacked_ld<T>(in, (size_t)(t0 + s) * in.row_stride + col) : tail[(size_t)(K - 1 + s) * channels + c];
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < kDeltaMaxTaps - 1; ++j) {
+    if (j < K - 1) tail[(size_t)j * channels + c] = keep[j];
+  }
+}
+
+constexpr int kDeltaWarps = 8;
+constexpr int kDeltaBatch = 8;       // tokens staged in shared memory at a time (one per warp for the k.q products)
+
+struct DeltaScanParams {
+  const float* q;     // [n_tokens, kv_heads, dk]
+  const float* k;
+  const float* v;     // [n_tokens, heads, dv]
+  const float* beta;  // [n_tokens, heads]
+  const float* g;
+  float* state;       // records; S of head h at h * dk * dv, row-major [dk, dv]
+  long long rec_stride;
+  float* out;         // [n_tokens, heads, dv]
+  const int* req_q_start;
+  const int* req_q_len;
+  const int* req_slot;
+  int* err;
+  int n_reqs, n_slots, heads, kv_heads, dk, dv;
+};
+
+__device__ __forceinline__ void cp_async4(float* dst, const float* src) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(d), "l"(src) : "memory");
+}
+
+// One block per (request, head, kCols value channels).  A thread owns kRows rows of one column of the
+// state in registers: lane -> (column = lane % kCols, row group within the warp = lane / kCols), the
+// warps hold further row groups.  Per token every thread forms its share of S^T k and S^T q from the
+// decayed state, the shares meet over shuffles and shared memory (added in a fixed order), and since
+//   o = (g S + k u^T)^T q = (g S)^T q + u (k . q)
+// one meeting per token is enough.  Tokens are staged in batches of kDeltaBatch through shared
+// memory, the next batch on its way (cp.async) while this one is worked through.
+template <int kCols, int kRows>
+__global__ void __launch_bounds__(kDeltaWarps * 32) delta_scan_kernel(DeltaScanParams p) {
+  constexpr int kSub = 32 / kCols;                     // row groups inside a warp
+  constexpr int kGroups = kDeltaWarps * kSub;
+  constexpr int kRowsAll = kGroups * kRows;            // rows the block can hold (>= dk)
+  __shared__ __align__(16) float s_q[2][kDeltaBatch][kRowsAll];
+  __shared__ __align__(16) float s_k[2][kDeltaBatch][kRowsAll];
+  __shared__ float s_v[2][kDeltaBatch][kCols];
+  __shared__ float s_beta[2][kDeltaBatch], s_g[2][kDeltaBatch], s_kq[kDeltaBatch];
+  __shared__ float s_red[2][2][kDeltaWarps][kCols];    // [parity][a | b][warp][column]
+  pdl_trigger();
+  pdl_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int col = lane % kCols, sub = lane / kCols;
+  const int group = warp * kSub + sub;
+  const int row0 = group * kRows;
+  const int r = blockIdx.z, h = blockIdx.y;
+  const int c0 = blockIdx.x * kCols;
+  const int hk = h / (p.heads / p.kv_heads);
+  const int n = p.req_q_len[r], t0 = p.req_q_start[r];
+  const int slot = p.req_slot[r];
+  if (slot < 0 || slot >= p.n_slots) { if (threadIdx.x == 0) set_error(p.err, kErrRequest, r, slot, p.n_slots); return; }
+  const int dk = p.dk, dv = p.dv;
+  const bool col_ok = c0 + col < dv;
+  float* S = p.state + (size_t)slot * p.rec_stride + (size_t)h * dk * dv;
+
+  float st[kRows];
+#pragma unroll
+  for (int i = 0; i < kRows; ++i) st[i] = (col_ok && row0 + i < dk) ? S[(size_t)(row0 + i) * dv + c0 + col] : 0.0f;
+  // rows beyond dk read q = k = 0 from shared memory and stay zero
+  for (int e = threadIdx.x; e < 2 * kDeltaBatch * kRowsAll; e += blockDim.x) {
+    (&s_q[0][0][0])[e] = 0.0f;
+    (&s_k[0][0][0])[e] = 0.0f;
+  }
+  __syncthreads();
+
+  auto stage = [&](int b0, int buf) {
+    const int cnt = min(kDeltaBatch, n - b0);
+    for (int e = threadIdx.x; e < cnt * dk; e += blockDim.x) {
+      const int i = e / dk, x = e - i * dk;
+      const size_t src = ((size_t)(t0 + b0 + i) * p.kv_heads + hk) * dk + x;
+      cp_async4(&s_q[buf][i][x], p.q + src);
+      cp_async4(&s_k[buf][i][x], p.k + src);
+    }
+    for (int e = threadIdx.x; e < cnt * kCols; e += blockDim.x) {
+      const int i = e / kCols, x = e - i * kCols;
+      if (c0 + x < dv) cp_async4(&s_v[buf][i][x], p.v + ((size_t)(t0 + b0 + i) * p.heads + h) * dv + c0 + x);
+    }
+    if (threadIdx.x < cnt) {
+      cp_async4(&s_beta[buf][threadIdx.x], p.beta + (size_t)(t0 + b0 + threadIdx.x) * p.heads + h);
+      cp_async4(&s_g[buf][threadIdx.x], p.g + (size_t)(t0 + b0 + threadIdx.x) * p.heads + h);
+    }
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+  };
+
+  if (n > 0) stage(0, 0);
+  int parity = 0;
+  for (int b0 = 0, buf = 0; b0 < n; b0 += kDeltaBatch, buf ^= 1) {
+    const int cnt = min(kDeltaBatch, n - b0);
+    if (b0 + kDeltaBatch < n) {
+      stage(b0 + kDeltaBatch, buf ^ 1);
+      asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+    }
+    __syncthreads();
+    // k . q of every staged token: one warp a token, lanes over the rows, added in a fixed order
+    if (warp < cnt) {
+      float d = 0.0f;
+      for (int x = lane; x < dk; x += 32) d += s_k[buf][warp][x] * s_q[buf][warp][x];
+      d = warp_sum(d);
+      if (lane == 0) s_kq[warp] = d;
+    }
+    __syncthreads();
+    for (int i = 0; i < cnt; ++i) {
+      const float gt = s_g[buf][i];
+      float a = 0.0f, b = 0.0f;
+#pragma unroll
+      for (int x = 0; x < kRows; ++x) {
+        st[x] *= gt;
+        a = fmaf(st[x], s_k[buf][i][row0 + x], a);
+        b = fmaf(st[x], s_q[buf][i][row0 + x], b);
+      }
+#pragma unroll
+      for (int off = kCols; off < 32; off <<= 1) {
+        a += __shfl_xor_sync(0xffffffffu, a, off);
+        b += __shfl_xor_sync(0xffffffffu, b, off);
+      }
+      if (sub == 0) { s_red[parity][0][warp][col] = a; s_red[parity][1][warp][col] = b; }
+      __syncthreads();
+      float at = 0.0f, bt = 0.0f;
+#pragma unroll
+      for (int w = 0; w < kDeltaWarps; ++w) { at += s_red[parity][0][w][col]; bt += s_red[parity][1][w][col]; }
+      const float u = s_beta[buf][i] * (s_v[buf][i][col] - at);
+#pragma unroll
+      for (int x = 0; x < kRows; ++x) st[x] = fmaf(s_k[buf][i][row0 + x], u, st[x]);
+      if (group == 0 && col_ok) p.out[((size_t)(t0 + b0 + i) * p.heads + h) * dv + c0 + col] = bt + u * s_kq[i];
+      parity ^= 1;
+    }
+    __syncthreads();      // the buffer is staged again two batches on; s_kq at the next batch
+  }
+#pragma unroll
+  for (int i = 0; i < kRows; ++i) {
+    if (col_ok && row0 + i < dk) S[(size_t)(row0 + i) * dv + c0 + col] = st[i];
+  }
+}
+
+}  // namespace tk
+
+TK_API int tk_delta_prepare(const void* x, const float* parts, int n_parts, long long part_stride, int row_stride,
+                            int q_off, int k_off, int v_off, int b_off, int a_off, const float* taps,
+                            const float* a_log, const float* dt_bias, float* state, long long rec_stride,
+                            long long tail_off, const int* tok_req, const int* req_q_start, const int* req_q_len,
+                            const int* req_slot, float* q_out, float* k_out, float* v_out, float* beta_out,
+                            float* g_out, int* err, int n_tokens, int n_reqs, int n_slots, int heads, int kv_heads,
+                            int dk, int dv, int n_taps, float unit_eps, float q_scale, int dtype, cudaStream_t stream) {
+  if (n_tokens <= 0 || n_reqs <= 0) return 0;
+  if ((x == nullptr) == (parts == nullptr) || heads < 1 || kv_heads < 1 || heads % kv_heads || dk < 1 || dv < 1 ||
+      n_taps < 1 || n_taps > tk::kDeltaMaxTaps || n_reqs > 65535) {
+    return (int)cudaErrorInvalidValue;
+  }
+  tk::DeltaPrepareParams p;
+  p.in.x = x; p.in.parts = parts; p.in.n_parts = n_parts; p.in.row_stride = row_stride; p.in.part_stride = part_stride;
+  p.q_off = q_off; p.k_off = k_off; p.v_off = v_off; p.b_off = b_off; p.a_off = a_off;
+  p.taps = taps; p.a_log = a_log; p.dt_bias = dt_bias; p.state = state; p.rec_stride = rec_stride; p.tail_off = tail_off;
+  p.tok_req = tok_req; p.req_q_start = req_q_start; p.req_slot = req_slot;
+  p.q_out = q_out; p.k_out = k_out; p.v_out = v_out; p.beta_out = beta_out; p.g_out = g_out; p.err = err;
+  p.n_tokens = n_tokens; p.n_reqs = n_reqs; p.n_slots = n_slots; p.heads = heads; p.kv_heads = kv_heads;
+  p.dk = dk; p.dv = dv; p.n_taps = n_taps; p.unit_eps = unit_eps; p.q_scale = q_scale;
+  const int units = 2 * kv_heads + heads;
+  dim3 grid(n_tokens, (units + tk::kDeltaPrepWarps - 1) / tk::kDeltaPrepWarps);
+  cudaError_t e = cudaSuccess;
+  TK_DISPATCH_DTYPE(dtype, T,
+                    e = tk::launch(tk::delta_prepare_kernel<T>, grid, dim3(tk::kDeltaPrepWarps * 32), 0, stream, p));
+  if (e != cudaSuccess || n_taps == 1) return (int)e;
+  const int hk = kv_heads * dk, hv = heads * dv;
+  dim3 tgrid((2 * hk + hv + 127) / 128, n_reqs);
+  TK_DISPATCH_DTYPE(dtype, T,
+                    e = tk::launch(tk::delta_tail_kernel<T>, tgrid, dim3(128), 0, stream, p.in, q_off, k_off, v_off,
+                                   state, rec_stride, tail_off, req_q_start, req_q_len, req_slot, n_slots, hk, hv,
+                                   n_taps));
+  return (int)e;
+}
+
+// Columns of the state that one block takes: fewer where the heads alone would leave SMs idle.  It
+// follows from the model's sizes only, never from the batch, so that a position's sums are always
+// added in the same order.
+TK_API int tk_delta_scan_cols(int heads, int dk, int dv) {
+  int cols = 32;
+  while (cols > 8 && (heads * ((dv + cols - 1) / cols) < 96 || cols / 2 >= dv)) cols /= 2;
+  (void)dk;
+  return cols;
+}
+
+TK_API int tk_delta_scan(const float* q, const float* k, const float* v, const float* beta, const float* g,
+                         float* state, long long rec_stride, float* out, const int* req_q_start,
+                         const int* req_q_len, const int* req_slot, int* err, int n_reqs, int n_slots, int heads,
+                         int kv_heads, int dk, int dv, int cols, cudaStream_t stream) {
+  if (n_reqs <= 0) return 0;
+  if (cols <= 0) cols = tk_delta_scan_cols(heads, dk, dv);
+  if (heads < 1 || kv_heads < 1 || heads % kv_heads || heads > 65535 || n_reqs > 65535 ||
+      (cols != 32 && cols != 16 && cols != 8)) {
+    return (int)cudaErrorInvalidValue;
+  }
+  const int groups = tk::kDeltaWarps * (32 / cols);
+  const int rows = (dk + groups - 1) / groups;
+  if (dk < 1 || dk > 256) return (int)cudaErrorInvalidValue;      // a block stages 256 key channels at most
+  tk::DeltaScanParams p;
+  p.q = q; p.k = k; p.v = v; p.beta = beta; p.g = g; p.state = state; p.rec_stride = rec_stride; p.out = out;
+  p.req_q_start = req_q_start; p.req_q_len = req_q_len; p.req_slot = req_slot; p.err = err;
+  p.n_reqs = n_reqs; p.n_slots = n_slots; p.heads = heads; p.kv_heads = kv_heads; p.dk = dk; p.dv = dv;
+  dim3 grid((dv + cols - 1) / cols, heads, n_reqs);
+  dim3 block(tk::kDeltaWarps * 32);
+  cudaError_t e = cudaSuccess;
+  // only the shapes whose rows fit 256 key channels a block are built
+#define TK_DELTA_LAUNCH(C, R) e = tk::launch(tk::delta_scan_kernel<C, R>, grid, block, 0, stream, p)
+  if (cols == 32) {
+    if (rows <= 4) TK_DELTA_LAUNCH(32, 4); else if (rows <= 8) TK_DELTA_LAUNCH(32, 8);
+    else if (rows <= 16) TK_DELTA_LAUNCH(32, 16); else TK_DELTA_LAUNCH(32, 32);
+  } else if (cols == 16) {
+    if (rows <= 4) TK_DELTA_LAUNCH(16, 4); else if (rows <= 8) TK_DELTA_LAUNCH(16, 8); else TK_DELTA_LAUNCH(16, 16);
+  } else {
+    if (rows <= 4) TK_DELTA_LAUNCH(8, 4); else TK_DELTA_LAUNCH(8, 8);
+  }
+#undef TK_DELTA_LAUNCH
+  return (int)e;
+}

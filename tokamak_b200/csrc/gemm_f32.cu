@@ -15,9 +15,14 @@ constexpr int kGemmBK = 16;
 
 __global__ void __launch_bounds__(256)
 gemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ W, float* __restrict__ C,
-                int M, int N, int K, int lda, int ldw, int ldc) {
+                int M, int N, int K, int lda, int ldw, int ldc, long long batch_a, long long batch_w,
+                long long batch_c) {
   pdl_trigger();
   pdl_wait();
+  // grid.z counts the products of a batch (one per head, say): each has its own A, W and C
+  A += (size_t)blockIdx.z * batch_a;
+  W += (size_t)blockIdx.z * batch_w;
+  C += (size_t)blockIdx.z * batch_c;
   __shared__ float sA[kGemmBK][kGemmBM + 4];
   __shared__ float sW[kGemmBK][kGemmBN + 4];
 
@@ -82,5 +87,19 @@ TK_API int tk_gemm_f32(const float* A, const float* W, float* C, int M, int N, i
   if (K < 0) return (int)cudaErrorInvalidValue;
   dim3 grid((N + tk::kGemmBN - 1) / tk::kGemmBN, (M + tk::kGemmBM - 1) / tk::kGemmBM);
   if (grid.y > 65535) return (int)cudaErrorInvalidValue;
-  return (int)tk::launch(tk::gemm_f32_kernel, grid, dim3(256), 0, stream, A, W, C, M, N, K, lda, ldw, ldc);
+  return (int)tk::launch(tk::gemm_f32_kernel, grid, dim3(256), 0, stream, A, W, C, M, N, K, lda, ldw, ldc, 0LL, 0LL,
+                         0LL);
+}
+
+// `batch` products of the same sizes: product b reads A + b * batch_a and W + b * batch_w and writes
+// C + b * batch_c (strides in elements).  Every output element is still one thread's ascending sum.
+TK_API int tk_gemm_f32_batched(const float* A, const float* W, float* C, int M, int N, int K, int lda, int ldw,
+                               int ldc, int batch, long long batch_a, long long batch_w, long long batch_c,
+                               cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || batch <= 0) return 0;
+  if (K < 0 || batch > 65535) return (int)cudaErrorInvalidValue;
+  dim3 grid((N + tk::kGemmBN - 1) / tk::kGemmBN, (M + tk::kGemmBM - 1) / tk::kGemmBM, batch);
+  if (grid.y > 65535) return (int)cudaErrorInvalidValue;
+  return (int)tk::launch(tk::gemm_f32_kernel, grid, dim3(256), 0, stream, A, W, C, M, N, K, lda, ldw, ldc, batch_a,
+                         batch_w, batch_c);
 }

@@ -32,10 +32,22 @@ _SIGNATURES: dict[str, list] = {
     "tk_rope_kv": [_P, _P, c_int, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
                    c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                    c_float, c_int, _P],
-    "tk_rope_table": [_P, _P, _P, c_int, c_int, _P],
+    "tk_rope_table": [_P, _P, _P, c_int, c_int, c_float, _P],
     "tk_attention_plain": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
                            c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                           c_float, c_int, c_int, c_float, _P, _P],
+                           c_float, c_int, c_int, c_float, _P, c_int, c_longlong, c_longlong, c_int, c_int, _P],
+    "tk_latent_prepare": [_P, _P, c_int, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                          _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
+                          c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, _P],
+    "tk_heads_gate": [_P, _P, _P, c_int, c_longlong, c_int, c_int, _P, c_int, c_int, c_int, c_int, _P],
+    "tk_delta_prepare": [_P, _P, c_int, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P,
+                         c_longlong, c_longlong, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
+                         c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, _P],
+    "tk_delta_scan": [_P, _P, _P, _P, _P, _P, c_longlong, _P, _P, _P, _P, _P,
+                      c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P],
+    "tk_delta_scan_cols": [c_int, c_int, c_int],
+    "tk_gemm_f32_batched": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_longlong, c_longlong,
+                            c_longlong, _P],
     "tk_branch_norm_add": [_P, _P, _P, c_int, c_longlong, _P, _P, _P, _P, _P, c_int, c_int, c_float, c_float,
                            c_int, _P],
     "tk_qkv_pairs": [_P, _P, c_int, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,

@@ -267,13 +267,13 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor, block: int = 0, activation:
            "swiglu")
 
 
-def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:
-    """``[tokens, len(inv_freq), 2]`` float32: (cos, sin) of ``float(position) * inv_freq[j]``."""
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, magnitude: float = 1.0) -> torch.Tensor:
+    """``[tokens, len(inv_freq), 2]`` float32: ``magnitude`` times (cos, sin) of ``float(position) * inv_freq[j]``."""
     _want(positions, torch.int32, "positions"); _want(inv_freq, torch.float32, "inv_freq")
     n, half = positions.numel(), inv_freq.numel()
     table = torch.empty((n, half, 2), dtype=torch.float32, device=positions.device)
     _check(_lib().tk_rope_table(positions.data_ptr(), inv_freq.data_ptr(), table.data_ptr(), n, 2 * half,
-                                   _stream()), "rope_table")
+                                   float(magnitude), _stream()), "rope_table")
     return table
 
 
@@ -346,34 +346,41 @@ def attention_plain(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v
     """Paged attention of a mixed batch; q is [N, Hq, d], out [N, Hq, dv] with dv the size of a
     value head (``v_cache`` is ``[pages, Hkv, page, dv]``).
 
-    ``items`` restricts the work to the listed token indices (rows of q and out).  ``softcap``
-    bounds the scaled scores (``cap * tanh(score / cap)``); ``sinks`` is one float32 per query
-    head whose exponential joins the softmax denominator."""
-    _want(q, None, "q"); _want(out, q.dtype, "out")
-    _want(k_cache, q.dtype, "k_cache"); _want(v_cache, q.dtype, "v_cache")
+    ``q`` is in the pages' type or float32, and may be any view whose last axis is dense (a
+    ``[Hq, N, d]`` tensor seen as ``[N, Hq, d]``).  ``v_cache`` may be a view of the leading ``dv``
+    elements of the key rows (a cache whose values are part of its keys).  ``items`` restricts the
+    work to the listed token indices (rows of q and out).  ``softcap`` bounds the scaled scores
+    (``cap * tanh(score / cap)``); ``sinks`` is one float32 per query head whose exponential joins
+    the softmax denominator."""
+    _want(out, k_cache.dtype, "out"); _want(k_cache, None, "k_cache")
+    if not q.is_cuda or q.dtype not in (k_cache.dtype, torch.float32) or q.stride(2) != 1:
+        raise KernelError("q must be a CUDA tensor in the pages' type or float32 with a dense last axis")
     n, hq, d = q.shape
     num_pages, hkv, page_size, dk = k_cache.shape
     dv = v_cache.shape[3]
-    if dk != d or v_cache.shape[:3] != k_cache.shape[:3] or out.shape != (n, hq, dv):
+    if dk != d or v_cache.shape[:3] != k_cache.shape[:3] or out.shape != (n, hq, dv) or v_cache.dtype != k_cache.dtype:
         raise KernelError("attention shape mismatch")
-    if dv > 256:
-        raise KernelError(f"value size {dv} is beyond the kernels' limit of 256")
+    v_stride = v_cache.stride(2)
+    if (not v_cache.is_cuda or v_cache.stride(3) != 1 or v_cache.stride(1) != page_size * v_stride
+            or v_cache.stride(0) != hkv * page_size * v_stride):
+        raise KernelError("v_cache must be laid out like pages, with a row stride of its own at most")
+    if max(d, dv) > 1024:
+        raise KernelError(f"head sizes {d} / {dv} are beyond the kernel's limit of 1024")
     if sinks is not None:
         _want(sinks, torch.float32, "sinks")
         if sinks.numel() != hq:
             raise KernelError("one sink per query head is needed")
     if hq % hkv:
         raise KernelError(f"{hq} query heads are not a multiple of {hkv} key/value heads")
-    if d > 256:
-        raise KernelError(f"head_dim {d} is beyond the kernels' limit of 256")
     _check(_lib().tk_attention_plain(q.data_ptr(), out.data_ptr(), k_cache.data_ptr(),
                                         v_cache.data_ptr(), positions.data_ptr(), tok_req.data_ptr(),
                                         req_slot.data_ptr(), block_table.data_ptr(), _ptr(items),
                                         err.data_ptr(), n if items is None else items.numel(),
                                         req_slot.numel(), hq, hkv, d, page_size,
                                         block_table.shape[1], num_pages, int(window or 0),
-                                        float(scale), dtype_code(q.dtype), dv, float(softcap or 0.0),
-                                        _ptr(sinks), _stream()),
+                                        float(scale), dtype_code(k_cache.dtype), dv, float(softcap or 0.0),
+                                        _ptr(sinks), dtype_code(q.dtype), q.stride(0), q.stride(1), d, v_stride,
+                                        _stream()),
            "attention_plain")
 
 
@@ -398,8 +405,9 @@ def branch_norm_add(resid: torch.Tensor, branch: torch.Tensor, post_weight: torc
                     layer_scale: torch.Tensor | None, branch_eps: float, next_weight: torch.Tensor | None,
                     out: torch.Tensor | None, next_eps: float = 0.0, rows: torch.Tensor | None = None) -> None:
     """``x = resid + rmsnorm(branch) * post_weight * layer_scale`` (written back unless ``rows``
-    selects rows), then ``out = rmsnorm(x) * next_weight`` if ``out`` is given.  ``branch`` is in
-    the activation type or float32 partial sums ``[parts, tokens, hidden]``."""
+    selects rows), then, if ``out`` is given, ``out = rmsnorm(x) * next_weight`` or, without
+    ``next_weight``, ``out = x`` in the activation type.  ``branch`` is in the activation type or
+    float32 partial sums ``[parts, tokens, hidden]``."""
     _want(resid, torch.float32, "resid")
     hidden = resid.shape[-1]
     dtype = out.dtype if out is not None else (branch.dtype if branch.dim() == 2 else torch.float32)
@@ -416,8 +424,8 @@ def branch_norm_add(resid: torch.Tensor, branch: torch.Tensor, post_weight: torc
     n_rows = rows.numel() if rows is not None else n
     if out is not None:
         _want(out, None, "out")
-        if next_weight is None or out.numel() < n_rows * hidden:
-            raise KernelError("out needs the weight of the norm that follows and room for the rows")
+        if out.numel() < n_rows * hidden:
+            raise KernelError("out needs room for the rows")
     _check(_lib().tk_branch_norm_add(resid.data_ptr(), _ptr(b), _ptr(parts), n_parts,
                                         parts.stride(0) if parts is not None else 0, _ptr(post_weight),
                                         _ptr(layer_scale), _ptr(next_weight), _ptr(out), _ptr(rows), n_rows, hidden,
@@ -902,6 +910,178 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) 
             raise KernelError("out has the wrong shape")
     _check(_lib().tk_gemm_f32(a.data_ptr(), w.data_ptr(), out.data_ptr(), m, n, k, k, k, n,
                                  _stream()), "gemm_f32")
+    return out
+
+
+def gemm_f32_heads(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """``out[h, t, :] = w[h] @ x[t, h, :]`` in true float32: ``x`` is a ``[tokens, heads, K]`` view with a
+    dense last axis, ``w`` ``[heads, M, K]`` contiguous; returns ``[heads, tokens, M]``."""
+    _want(w, torch.float32, "w")
+    n, heads, k = x.shape
+    if x.dtype != torch.float32 or not x.is_cuda or x.stride(2) != 1 or w.shape[0] != heads or w.shape[2] != k:
+        raise KernelError("x must be float32 [tokens, heads, K] with a dense last axis and w [heads, M, K]")
+    m = w.shape[1]
+    out = torch.empty((heads, n, m), dtype=torch.float32, device=x.device)
+    _check(_lib().tk_gemm_f32_batched(x.data_ptr(), w.data_ptr(), out.data_ptr(), n, m, k, x.stride(0), k, m, heads,
+                                         x.stride(1), m * k, n * m, _stream()), "gemm_f32_heads")
+    return out
+
+
+def _stacked(x: torch.Tensor, like: torch.dtype, name: str) -> tuple:
+    """(pointer | None, parts pointer | None, parts, part stride, tokens, row length) of a product's result."""
+    t, parts, n_parts, n, row = _parts_of(x, like, name)
+    return _ptr(t), _ptr(parts), n_parts, (parts.stride(0) if parts is not None else 0), n, row
+
+
+def latent_prepare(proj: torch.Tensor, cache: torch.Tensor, positions: torch.Tensor, tok_req: torch.Tensor,
+                   req_slot: torch.Tensor, block_table: torch.Tensor, err: torch.Tensor, *, kv_off: int, rank: int,
+                   rot: int, kv_norm_w: torch.Tensor, eps: float, table: torch.Tensor | None = None,
+                   q_abs: torch.Tensor | None = None, q_off: int = 0, q_head_cols: int = 0, q_rot_off: int = 0,
+                   cq_off: int = 0, cq_norm_w: torch.Tensor | None = None,
+                   req_q_len: torch.Tensor | None = None, req_kv_len: torch.Tensor | None = None):
+    """A latent cache's rows for the step's tokens, and what the queries need, from the columns of the
+    stacked projection ``proj`` (the cache's type, or float32 partial sums).
+
+    Columns ``kv_off .. + rank`` are RMS-normed with ``kv_norm_w`` (the latent), the ``rot`` columns
+    behind them are the shared key part, whose first ``2 * table.shape[1]`` elements turn as
+    neighbouring pairs by the (cos, sin) of ``table``; both go to the token's row of ``cache``
+    ``[pages, 1, page, rank + rot]``.  With ``q_abs`` (float32 ``[heads, tokens, rank]``) the query rows
+    ``[tokens, heads, rank + rot]`` are returned in float32: ``q_abs`` and the turned columns
+    ``q_off + h * q_head_cols + q_rot_off .. + rot``.  With ``cq_norm_w`` the columns ``cq_off .. +
+    len(cq_norm_w)`` are RMS-normed into a second result ``[tokens, len(cq_norm_w)]``.
+    Returns ``(query rows | None, normed query latent | None)``."""
+    _want(cache, None, "cache"); _want(kv_norm_w, torch.float32, "kv_norm_w")
+    x, parts, n_parts, part_stride, n, row = _stacked(proj, cache.dtype, "proj")
+    num_pages, one, page_size, width = cache.shape
+    if one != 1 or width != rank + rot or kv_norm_w.numel() != rank or kv_off < 0 or kv_off + width > row:
+        raise KernelError("the cache rows or the latent's columns do not match the sizes")
+    pairs = 0
+    if table is not None:
+        _want(table, torch.float32, "table")
+        pairs = table.shape[1]
+        if table.shape[0] != n or 2 * pairs > rot:
+            raise KernelError("the rotation table does not match the tokens or the rotated part")
+    heads, q_lat = 0, None
+    if q_abs is not None:
+        _want(q_abs, torch.float32, "q_abs")
+        heads = q_abs.shape[0]
+        if q_abs.shape != (heads, n, rank) or q_off < 0 or q_off + (heads - 1) * q_head_cols + q_rot_off + rot > row:
+            raise KernelError("q_abs must be [heads, tokens, rank] and the rotated query columns inside the row")
+        q_lat = torch.empty((n, heads, width), dtype=torch.float32, device=cache.device)
+    cq, cq_rank = None, 0
+    if cq_norm_w is not None:
+        _want(cq_norm_w, torch.float32, "cq_norm_w")
+        cq_rank = cq_norm_w.numel()
+        if cq_off < 0 or cq_off + cq_rank > row:
+            raise KernelError("the query latent's columns lie outside the row")
+        cq = torch.empty((n, cq_rank), dtype=cache.dtype, device=cache.device)
+    for name, t in (("positions", positions), ("tok_req", tok_req), ("req_slot", req_slot), ("block_table", block_table)):
+        _want(t, torch.int32, name)
+    _check(_lib().tk_latent_prepare(x, parts, n_parts, part_stride, row, kv_off, q_off, q_head_cols, q_rot_off, cq_off,
+                                       cq_rank, kv_norm_w.data_ptr(), _ptr(cq_norm_w), _ptr(cq), _ptr(q_abs), _ptr(q_lat),
+                                       cache.data_ptr(), _ptr(table), positions.data_ptr(), tok_req.data_ptr(),
+                                       req_slot.data_ptr(), block_table.data_ptr(), _ptr(req_q_len), _ptr(req_kv_len),
+                                       err.data_ptr(), n, req_slot.numel(), heads, rank, rot, pairs, page_size,
+                                       block_table.shape[1], num_pages, float(eps), dtype_code(cache.dtype), _stream()),
+           "latent_prepare")
+    return q_lat, cq
+
+
+def heads_gate(x: torch.Tensor, proj: torch.Tensor | None = None, g_off: int = 0) -> torch.Tensor:
+    """``y[t, h * dv + e] = x[h, t, e] * sigmoid(proj[t, g_off + h * dv + e])`` (``proj=None``: no gate):
+    per-head results ``[heads, tokens, dv]`` back as token rows ``[tokens, heads * dv]``."""
+    _want(x, None, "x")
+    heads, n, dv = x.shape
+    gx = gparts = None
+    n_parts, part_stride, row = 0, 0, 0
+    if proj is not None:
+        gx, gparts, n_parts, part_stride, n2, row = _stacked(proj, x.dtype, "proj")
+        if n2 != n or g_off < 0 or g_off + heads * dv > row:
+            raise KernelError("the gate columns lie outside the row")
+    else:
+        g_off = -1
+    y = torch.empty((n, heads * dv), dtype=x.dtype, device=x.device)
+    _check(_lib().tk_heads_gate(x.data_ptr(), gx, gparts, n_parts, part_stride, row, g_off, y.data_ptr(), n, heads, dv,
+                                   dtype_code(x.dtype), _stream()), "heads_gate")
+    return y
+
+
+def delta_record_floats(heads: int, kv_heads: int, key_dim: int, value_dim: int, taps: int) -> tuple[int, int]:
+    """``(floats of a request's record, where the convolution's tail starts)``: the state of every head,
+    then the last ``taps - 1`` inputs of every q, k and v channel."""
+    state = heads * key_dim * value_dim
+    return state + (taps - 1) * (2 * kv_heads * key_dim + heads * value_dim), state
+
+
+def delta_prepare(proj: torch.Tensor, taps: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor,
+                  records: torch.Tensor, tok_req: torch.Tensor, req_q_start: torch.Tensor, req_q_len: torch.Tensor,
+                  req_slot: torch.Tensor, err: torch.Tensor, *, dtype: torch.dtype, q_off: int, k_off: int, v_off: int,
+                  b_off: int, a_off: int, heads: int, kv_heads: int, key_dim: int, value_dim: int, unit_eps: float,
+                  q_scale: float) -> tuple:
+    """The float32 inputs of the delta-rule recurrence from the columns of the stacked projection
+    ``proj`` (type ``dtype``, or float32 partial sums): short causal convolution (``taps`` float32
+    ``[channels, K]``, channels in the order q, k, v) and silu on q, k and v, q and k heads scaled to
+    unit length (q also by ``q_scale``), ``beta = sigmoid(b)`` and ``g = exp(-exp(a_log) softplus(a +
+    dt_bias))`` per head.  The convolution reads the inputs before the step from the tail of the
+    requests' ``records`` (float32 ``[slots, floats]``, see :func:`delta_record_floats`) and moves the tail on.
+    Returns ``(q [N, Hk, dk], k [N, Hk, dk], v [N, H, dv], beta [N, H], g [N, H])``."""
+    _want(taps, torch.float32, "taps"); _want(a_log, torch.float32, "a_log"); _want(dt_bias, torch.float32, "dt_bias")
+    _want(records, torch.float32, "records")
+    x, parts, n_parts, part_stride, n, row = _stacked(proj, dtype, "proj")
+    hk, hv = kv_heads * key_dim, heads * value_dim
+    channels, k_taps = taps.shape
+    floats, tail_off = delta_record_floats(heads, kv_heads, key_dim, value_dim, k_taps)
+    if channels != 2 * hk + hv or records.dim() != 2 or records.shape[1] != floats:
+        raise KernelError("taps must be [q + k + v channels, K] and the records sized by delta_record_floats")
+    if a_log.numel() != heads or dt_bias.numel() != heads:
+        raise KernelError("one A_log and one dt_bias per head are needed")
+    for off, size in ((q_off, hk), (k_off, hk), (v_off, hv), (b_off, heads), (a_off, heads)):
+        if off < 0 or off + size > row:
+            raise KernelError("a column range lies outside the row")
+    for name, t in (("tok_req", tok_req), ("req_q_start", req_q_start), ("req_q_len", req_q_len), ("req_slot", req_slot)):
+        _want(t, torch.int32, name)
+    dev = records.device
+    q = torch.empty((n, kv_heads, key_dim), dtype=torch.float32, device=dev)
+    k = torch.empty_like(q)
+    v = torch.empty((n, heads, value_dim), dtype=torch.float32, device=dev)
+    beta = torch.empty((n, heads), dtype=torch.float32, device=dev)
+    g = torch.empty_like(beta)
+    _check(_lib().tk_delta_prepare(x, parts, n_parts, part_stride, row, q_off, k_off, v_off, b_off, a_off,
+                                      taps.data_ptr(), a_log.data_ptr(), dt_bias.data_ptr(), records.data_ptr(), floats,
+                                      tail_off, tok_req.data_ptr(), req_q_start.data_ptr(), req_q_len.data_ptr(),
+                                      req_slot.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), beta.data_ptr(),
+                                      g.data_ptr(), err.data_ptr(), n, req_slot.numel(), records.shape[0], heads,
+                                      kv_heads, key_dim, value_dim, k_taps, float(unit_eps), float(q_scale),
+                                      dtype_code(dtype), _stream()), "delta_prepare")
+    global LAUNCHES
+    LAUNCHES += 1 if k_taps > 1 else 0       # the kernel that moves the tail on
+    return q, k, v, beta, g
+
+
+def delta_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: torch.Tensor, g: torch.Tensor,
+               records: torch.Tensor, req_q_start: torch.Tensor, req_q_len: torch.Tensor, req_slot: torch.Tensor,
+               err: torch.Tensor, *, cols: int = 0) -> torch.Tensor:
+    """The gated delta rule ``S = g S; u = beta (v - S^T k); S += k u^T; o = S^T q`` over every request's
+    tokens of the step; the states ``[heads, dk, dv]`` lead the requests' float32 ``records`` and are
+    advanced in place.  Returns ``o`` float32 ``[tokens, heads, dv]``.  ``cols`` is the number of value
+    channels a block takes (32, 16 or 8; 0: what the sizes of the heads suggest)."""
+    for name, t in (("q", q), ("k", k), ("v", v), ("beta", beta), ("g", g), ("records", records)):
+        _want(t, torch.float32, name)
+    n, kv_heads, dk = q.shape
+    _, heads, dv = v.shape
+    if k.shape != q.shape or v.shape[0] != n or beta.shape != (n, heads) or g.shape != (n, heads) or heads % kv_heads:
+        raise KernelError("the recurrence's inputs do not match one another")
+    if records.dim() != 2 or records.shape[1] < heads * dk * dv:
+        raise KernelError("a record is too short for the state")
+    if dk > 256:
+        raise KernelError(f"key size {dk} is beyond the kernel's limit of 256")
+    for name, t in (("req_q_start", req_q_start), ("req_q_len", req_q_len), ("req_slot", req_slot)):
+        _want(t, torch.int32, name)
+    out = torch.empty((n, heads, dv), dtype=torch.float32, device=records.device)
+    _check(_lib().tk_delta_scan(q.data_ptr(), k.data_ptr(), v.data_ptr(), beta.data_ptr(), g.data_ptr(),
+                                   records.data_ptr(), records.shape[1], out.data_ptr(), req_q_start.data_ptr(),
+                                   req_q_len.data_ptr(), req_slot.data_ptr(), err.data_ptr(), req_slot.numel(),
+                                   records.shape[0], heads, kv_heads, dk, dv, int(cols), _stream()), "delta_scan")
     return out
 
 

@@ -17,9 +17,9 @@
 
 namespace tk {
 
-// table[t, j] = (cos, sin)(float(positions[t]) * inv_freq[j])
+// table[t, j] = magnitude * (cos, sin)(float(positions[t]) * inv_freq[j])
 __global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq,
-                                  float2* __restrict__ table, int n_tokens, int half) {
+                                  float2* __restrict__ table, int n_tokens, int half, float magnitude) {
   pdl_trigger();
   pdl_wait();
   const int idx = blockIdx.x * blockDim.x + threadIdx.x;
@@ -28,7 +28,7 @@ __global__ void rope_table_kernel(const int* __restrict__ positions, const float
   const float ang = (float)positions[t] * inv_freq[j];
   float s, c;
   sincosf(ang, &s, &c);
-  table[idx] = make_float2(c, s);
+  table[idx] = make_float2(c * magnitude, s * magnitude);
 }
 
 struct RopeKvParams {
@@ -400,13 +400,13 @@ static cudaError_t launch_rope_chunk(const RopeKvParams& p, int tph, long long t
 }  // namespace tk
 
 TK_API int tk_rope_table(const int* positions, const float* inv_freq, float* table, int n_tokens,
-                         int rotary_dim, cudaStream_t stream) {
+                         int rotary_dim, float magnitude, cudaStream_t stream) {
   if (n_tokens <= 0 || rotary_dim <= 0) return 0;
   if (rotary_dim & 1) return (int)cudaErrorInvalidValue;
   const int half = rotary_dim / 2;
   const int total = n_tokens * half;
   return (int)tk::launch(tk::rope_table_kernel, dim3((total + 255) / 256), dim3(256), 0, stream, positions,
-                         inv_freq, (float2*)table, n_tokens, half);
+                         inv_freq, (float2*)table, n_tokens, half, magnitude);
 }
 
 TK_API int tk_rope_kv(const void* qkv, const float* qkv_parts, int n_parts, void* q_out, void* k_cache,

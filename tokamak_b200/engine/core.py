@@ -131,7 +131,7 @@ class EngineCore:
         if not 0.0 < utilization <= 1.0:
             raise ValueError(f"memory_utilization must be in (0, 1], got {utilization}")
         elem = 4 if self.dtype == torch.float32 else 2
-        per_token = sum(need.n_kv_heads * (need.head_dim + need.value_dim) * elem
+        per_token = sum(need.n_kv_heads * need.stored_dim * elem
                         for need in self.model.cache_needs().values() if isinstance(need, KVPagesNeed))
         smallest = -(-self.max_seq_len // page_size) * page_size
         if per_token == 0:

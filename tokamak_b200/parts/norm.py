@@ -68,3 +68,72 @@ class RMSNorm:
         out = torch.empty((n, self.spec.dim), dtype=self.rt.dtype, device=resid.device)
         ops.add_rmsnorm(resid, delta, self.weight, out, self.spec.eps, rows)
         return out
+
+
+@dataclass(frozen=True)
+class OffsetRMSNormSpec:
+    """An RMS norm whose weight is stored around zero: the factor is ``1 + w``."""
+
+    dim: int
+    eps: float
+    kind: str = "rmsnorm_offset"
+
+
+@NORMS.register("rmsnorm_offset")
+class OffsetRMSNorm(RMSNorm):
+    """``(1 + w) * x * rsqrt(mean(x^2) + eps)``: the stored tensor is the weight's distance from one.
+    ``1 + w`` is formed once, in float32, when the part is built; everything else is :class:`RMSNorm`."""
+
+    def __init__(self, spec: OffsetRMSNormSpec, name: str, tensors: dict[str, torch.Tensor], rt: Runtime):
+        self.spec = spec
+        self.rt = rt
+        self.weight = (1.0 + tensors[name].float()).contiguous()
+
+    @staticmethod
+    def expected_tensors(spec: OffsetRMSNormSpec, name: str) -> dict[str, TensorReq]:
+        return {name: TensorReq((spec.dim,), role="bias")}
+
+
+@dataclass(frozen=True)
+class CastNormSpec:
+    """No normalisation: the seat of a norm in front of a sublayer that reads the residual stream itself."""
+
+    dim: int
+    kind: str = "cast"
+
+
+@NORMS.register("cast")
+class CastNorm:
+    """Joins the pending branch to the float32 residual stream and hands the rows on unnormalised,
+    rounded to the engine's dtype (the sublayer's products read that type).  It has no tensor."""
+
+    GRAPH_SAFE = True
+
+    def __init__(self, spec: CastNormSpec, name: str, tensors: dict[str, torch.Tensor], rt: Runtime):
+        self.spec = spec
+        self.rt = rt
+
+    @staticmethod
+    def expected_tensors(spec: CastNormSpec, name: str) -> dict[str, TensorReq]:
+        return {}
+
+    def weight_bytes(self) -> int:
+        return 0
+
+    def add_norm(self, resid: torch.Tensor, delta, rows: torch.Tensor | None = None):
+        if isinstance(delta, OwedNorm):
+            delta = None        # its branch is in the stream already
+        if isinstance(delta, NormedBranch):
+            n = rows.numel() if rows is not None else resid.shape[0]
+            out = torch.empty((n, self.spec.dim), dtype=self.rt.dtype, device=resid.device)
+            ops.branch_norm_add(resid, delta.x, delta.weight, delta.layer_scale, delta.eps, None, out, 0.0, rows)
+            return out
+        if delta is not None:
+            from .base import sum_parts
+            delta = sum_parts(delta, torch.float32)
+            if rows is None:
+                resid.add_(delta)
+            else:
+                return (resid.index_select(0, rows.long()) + delta.index_select(0, rows.long())).to(self.rt.dtype)
+        x = resid if rows is None else resid.index_select(0, rows.long())
+        return x.to(self.rt.dtype, copy=True)

@@ -60,13 +60,45 @@ class RopeNeox:
 
 
 @dataclass(frozen=True)
+class YarnScaling:
+    """Stretching of a rotary encoding beyond the length it was trained for: pairs that turn fewer
+    than ``slow`` times over ``original`` positions have their frequency divided by ``factor``, pairs
+    that turn more than ``fast`` times keep it, a linear ramp over the pair index lies between; cosine
+    and sine are multiplied by ``0.1 ln(factor) + 1``."""
+
+    factor: float
+    original: float
+    fast: float
+    slow: float
+
+
+@dataclass(frozen=True)
 class RopePairsSpec:
     """Rotation of neighbouring pairs (elements 2i and 2i+1) over the first ``rotary_dim``
-    elements of a head; the rest passes unrotated."""
+    elements of a head; the rest passes unrotated.  ``yarn`` stretches the frequencies."""
 
     rotary_dim: int
     theta: float
+    yarn: YarnScaling | None = None
     kind: str = "rope_pairs"
+
+
+def yarn_frequencies(rotary_dim: int, theta: float, yarn: YarnScaling | None) -> tuple[torch.Tensor, float]:
+    """``(float64 frequencies [rotary_dim / 2], factor on cosine and sine)``.  With
+    ``where(t) = rotary_dim ln(original / (2 pi t)) / (2 ln theta)``, the pair index at which a pair turns
+    ``t`` times over the original length, the ramp runs from ``lo = max(floor(where(fast)), 0)`` to
+    ``hi = min(ceil(where(slow)), rotary_dim - 1)``: ``ramp = clamp((i - lo) / max(hi - lo, 0.001), 0, 1)`` and
+    ``f = f0 / factor * ramp + f0 * (1 - ramp)``."""
+    import math
+    idx = torch.arange(0, rotary_dim, 2, dtype=torch.float64)
+    freq = float(theta) ** (-idx / max(rotary_dim, 1))
+    if yarn is None:
+        return freq, 1.0
+    where = lambda turns: rotary_dim * math.log(yarn.original / (2.0 * math.pi * turns)) / (2.0 * math.log(theta))
+    lo = max(math.floor(where(yarn.fast)), 0)
+    hi = min(math.ceil(where(yarn.slow)), rotary_dim - 1)
+    ramp = ((idx / 2 - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+    return freq / yarn.factor * ramp + freq * (1.0 - ramp), 0.1 * math.log(yarn.factor) + 1.0
 
 
 @POSITIONS.register("rope_pairs")
@@ -82,8 +114,8 @@ class RopePairs:
         if spec.rotary_dim % 2 or spec.rotary_dim < 0:
             raise ValueError(f"the rotated part of a head must be even, got {spec.rotary_dim}")
         self.spec = spec
-        idx = torch.arange(0, spec.rotary_dim, 2, dtype=torch.float64)
-        self.inv_freq = (float(spec.theta) ** (-idx / max(spec.rotary_dim, 1))).to(torch.float32).to(rt.device)
+        freq, self.magnitude = yarn_frequencies(spec.rotary_dim, spec.theta, spec.yarn)
+        self.inv_freq = freq.to(torch.float32).to(rt.device)
 
     @staticmethod
     def expected_tensors(spec: RopePairsSpec) -> dict:
@@ -95,7 +127,7 @@ class RopePairs:
         key = ("rope_table", self.spec)
         table = step.scratch.get(key)
         if table is None:
-            table = ops.rope_table(step.positions, self.inv_freq)
+            table = ops.rope_table(step.positions, self.inv_freq, self.magnitude)
             step.scratch[key] = table
         return table, self.spec.rotary_dim
 
