@@ -316,6 +316,67 @@ def test_attention_over_latent_rows_with_stand_out_keys(dtype, rank, dr, window)
     assert torch.equal(out2, out)
 
 
+@pytest.mark.parametrize("H,rank,dr,window", [(3, 64, 32, None), (16, 128, 64, 70), (4, 512, 64, None), (5, 16, 0, 1),
+                                              (70, 32, 16, 9)])
+def test_tensor_core_attention_over_latent_rows(H, rank, dr, window):
+    """The kernel that stacks a token's heads as rows of a tile: a portion of a prompt (two 64-token tiles,
+    the second one ragged) beside single tokens of two other requests whose keys are cut into 1, 2 and 5
+    shares; every query token makes one key stand out for head 1: far back, at a page border, the first or
+    the last key inside its window, the first one outside."""
+    from types import SimpleNamespace
+    from tokamak_b200.csrc import ops
+    page, ctx, scale = 8, 150, 0.4
+    width = rank + dr
+    assert ops.latent_kernel_takes(width, rank)
+    g = torch.Generator().manual_seed(H + rank)
+    w = window or ctx
+    seqs = [(0.3 * torch.randn(n, width, generator=g)).bfloat16() for n in (ctx, 131, 64)]
+    n_pages = sum(-(-len(x) // page) for x in seqs)
+    perm = torch.randperm(n_pages + 2, generator=g)
+    cache = torch.zeros(n_pages + 2, 1, page, width, dtype=torch.bfloat16, device="cuda")
+    table = torch.full((4, 32), -1, dtype=torch.int32)
+    slots, at = [2, 0, 3], 0
+    for x, slot in zip(seqs, slots):
+        for p in range(len(x)):
+            if p % page == 0:
+                table[slot, p // page] = perm[at]; at += 1
+            cache[table[slot, p // page], 0, p % page] = dev(x[p])
+    q_len = [70, 1, 1]
+    kv_len = [len(x) for x in seqs]
+    starts = [0, 70, 71]
+    positions = list(range(ctx - 70, ctx)) + [130, 63]
+    tok_req = [0] * 70 + [1, 2]
+    q = 0.2 * torch.randn(72, H, width, generator=g)
+    targets = []
+    for t, (pos, r) in enumerate(zip(positions, tok_req)):
+        choices = [pos, max(0, pos - w + 1), max(0, pos - w), (pos // page) * page, max(0, (pos // page) * page - 1), 0, pos // 2]
+        far = choices[t % len(choices)]
+        key = seqs[r][far].double()
+        q[t, 1 % H] = (key * 25.0 / scale / key.norm() ** 2).float()
+        targets.append(far)
+    sinks = torch.linspace(-1.0, 2.0, H) if window is None else None
+    step = SimpleNamespace(positions=dev(torch.tensor(positions, dtype=torch.int32)), tok_req=dev(torch.tensor(tok_req, dtype=torch.int32)),
+                           req_q_start=i32(*starts), req_q_len=i32(*q_len), req_kv_len=i32(*kv_len), req_slot=i32(*slots),
+                           err=new_err())
+    want = torch.zeros(72, H, rank, dtype=torch.float64)
+    for t, (pos, r) in enumerate(zip(positions, tok_req)):
+        want[t] = _attend(q[t].bfloat16().double(), seqs[r].double(), pos + 1, scale, window,
+                          sinks.double() if sinks is not None else None, rank)
+    kw = dict(scale=scale, window=window, sinks=dev(sinks) if sinks is not None else None)
+    tiles = i32(0, 1, 0, 0)                    # (request row, tile) pairs, the ragged tile first
+    for q_dev in (dev(q), dev(q.bfloat16()), dev(q.transpose(0, 1).contiguous()).transpose(0, 1)):
+        for n_splits in (1, 2, 5):
+            out = torch.zeros(72, H, rank, dtype=torch.bfloat16, device="cuda")
+            ops.attention_latent(q_dev, out, cache, rank, step, dev(table), tiles=tiles, **kw)
+            ops.attention_latent(q_dev, out, cache, rank, step, dev(table), items=i32(71, 70), n_splits=n_splits, **kw)
+            assert step.err.cpu().tolist()[0] == 0
+            close(out, want, "bfloat16", scale=2.0)
+            for t, far in enumerate(targets):
+                seen = positions[t] - far < w
+                near = (out[t, 1 % H].cpu().double() - seqs[tok_req[t]][far, :rank].double()).abs().max().item()
+                assert (near < 0.05) == seen, (t, positions[t], far, near)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_per_head_products_and_the_gated_way_back(dtype):
     from tokamak_b200.csrc import ops

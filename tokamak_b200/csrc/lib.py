@@ -39,6 +39,9 @@ _SIGNATURES: dict[str, list] = {
     "tk_latent_prepare": [_P, _P, c_int, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                           _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
                           c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, _P],
+    "tk_attention_latent": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_longlong, c_longlong,
+                            c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, _P],
+    "tk_attention_latent_takes": [c_int, c_int],
     "tk_heads_gate": [_P, _P, _P, c_int, c_longlong, c_int, c_int, _P, c_int, c_int, c_int, c_int, _P],
     "tk_delta_prepare": [_P, _P, c_int, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P,
                          c_longlong, c_longlong, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,

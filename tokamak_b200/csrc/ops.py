@@ -384,6 +384,58 @@ def attention_plain(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v
            "attention_plain")
 
 
+def latent_kernel_takes(d: int, dv: int) -> bool:
+    """Whether :func:`attention_latent` takes cache rows of ``d`` elements whose leading ``dv`` are the values."""
+    return bool(library().tk_attention_latent_takes(d, dv))
+
+
+def latent_decode_splits(device: torch.device, n_items: int, max_kv_len: int, window: int | None) -> int:
+    """Shares that the keys of a single token are cut into: enough blocks for two rounds over the SMs,
+    at least four 64-key tiles a share.  It follows from the step's bucket, not from its lengths."""
+    tiles = -(-min(max_kv_len, window or max_kv_len) // 64) + 1
+    want = -(-2 * sm_count(device) // max(1, n_items))
+    return max(1, min(want, tiles // 4))
+
+
+def attention_latent(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, dv: int, step, block_table: torch.Tensor,
+                     *, scale: float, window: int | None = None, sinks: torch.Tensor | None = None,
+                     tiles: torch.Tensor | None = None, items: torch.Tensor | None = None, n_splits: int = 1) -> None:
+    """Attention over a latent cache on the tensor cores: ``cache`` is ``[pages, 1, page, d]`` bfloat16, the
+    values are the rows' leading ``dv`` elements, ``q`` is ``[N, H, d]`` (float32 or bfloat16, any view with a
+    dense last axis), ``out`` ``[N, H, dv]`` bfloat16.  Either ``tiles`` (int32 pairs of request row and
+    64-token tile: prompt portions) or ``items`` (token indices of requests that bring one token, whose
+    keys are cut into ``n_splits`` shares) says what to work on; ``step`` is the batch description."""
+    _want(out, torch.bfloat16, "out"); _want(cache, torch.bfloat16, "cache")
+    n, heads, d = q.shape
+    num_pages, one, page_size, dk = cache.shape
+    if one != 1 or dk != d or out.shape != (n, heads, dv) or not latent_kernel_takes(d, dv):
+        raise KernelError("the latent attention kernel does not take these sizes")
+    if not q.is_cuda or q.dtype not in (torch.float32, torch.bfloat16) or q.stride(2) != 1:
+        raise KernelError("q must be a CUDA tensor, float32 or bfloat16, with a dense last axis")
+    _want_sinks(sinks, heads)
+    if (tiles is None) == (items is None):
+        raise KernelError("either tiles or items")
+    part_o = part_ml = None
+    if tiles is not None:
+        _want(tiles, torch.int32, "tiles")
+        n_work, n_splits = tiles.numel() // 2, 1
+    else:
+        _want(items, torch.int32, "items")
+        n_work = items.numel()
+        if n_splits > 1:
+            part_o = torch.empty((n_work, heads, n_splits, dv), dtype=torch.float32, device=q.device)
+            part_ml = torch.empty((n_work, heads, n_splits, 2), dtype=torch.float32, device=q.device)
+    global LAUNCHES
+    _check(_lib().tk_attention_latent(q.data_ptr(), out.data_ptr(), cache.data_ptr(), _ptr(sinks), _ptr(tiles), _ptr(items),
+                                         step.positions.data_ptr(), step.tok_req.data_ptr(), step.req_q_start.data_ptr(),
+                                         step.req_q_len.data_ptr(), step.req_kv_len.data_ptr(), step.req_slot.data_ptr(),
+                                         block_table.data_ptr(), _ptr(part_o), _ptr(part_ml), step.err.data_ptr(),
+                                         q.stride(0), q.stride(1), dtype_code(q.dtype), n_work, step.req_slot.numel(),
+                                         heads, d, dv, page_size, block_table.shape[1], num_pages, int(window or 0),
+                                         int(n_splits), float(scale), _stream()), "attention_latent")
+    LAUNCHES += 1 if n_splits > 1 else 0        # the kernel that adds the shares up
+
+
 def _want_sinks(sinks: torch.Tensor | None, n_q_heads: int) -> None:
     if sinks is not None:
         _want(sinks, torch.float32, "sinks")

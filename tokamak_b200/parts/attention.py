@@ -276,7 +276,8 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, cache_view, step, *, sca
     query head) adds ``exp(sink)`` to every softmax denominator.  ``out`` is ``[N, Hq, dv]`` where
     the value heads have a size of their own.
 
-    Chooses the kernels.  bfloat16 with a head_dim the tiled kernels take: single next
+    Chooses the kernels.  A latent cache in bfloat16 goes to the tensor-core kernel that stacks the heads
+    of a token (``csrc/attention_latent.cu``).  bfloat16 with a head_dim the tiled kernels take: single next
     tokens go to the split-K decode kernel, portions of prompts to the tcgen05 flash
     prefill kernel (or to the mma.sync one for page sizes it does not take).  float32,
     and every other shape, runs on the general kernel.
@@ -287,6 +288,19 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, cache_view, step, *, sca
     bf16 = q.dtype == torch.bfloat16
     n_dec = step.decode_items.numel()
     n_pf = step.prefill_items.numel()
+    dv = cache_view.v.shape[3]
+    if (hkv == 1 and cache_view.k.dtype == torch.bfloat16 and cache_view.v.data_ptr() == cache_view.k.data_ptr()
+            and cache_view.v.stride(2) == d and softcap is None and ops.latent_kernel_takes(d, dv)):
+        # a latent cache (one row a position for all heads, the values inside the keys): the heads of a
+        # token are rows of one tile of the tensor-core kernel, which reads every key once for all of them
+        if n_dec:
+            ops.attention_latent(q, out, cache_view.k, dv, step, cache_view.table, scale=scale, window=window, sinks=sinks,
+                                 items=step.decode_items,
+                                 n_splits=ops.latent_decode_splits(q.device, n_dec, step.max_kv_len, window))
+        if n_pf:
+            ops.attention_latent(q, out, cache_view.k, dv, step, cache_view.table, scale=scale, window=window, sinks=sinks,
+                                 tiles=step.prefill_tiles)
+        return
     # the tiled kernels take heads of one size for keys and values; of the two prefill kernels the
     # tcgen05 one knows caps and sinks
     same_size = cache_view.v.shape[3] == d
