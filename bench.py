@@ -812,11 +812,27 @@ def qwen3_twin(s: dict) -> dict:
                 vocab_size=s["vocab"], use_sliding_window=True, sliding_window=s["window"], max_window_layers=0)
 
 
-def _time_us(run, iters: int = 20) -> float:
+def _time_us(run, iters: int = 20, graph: bool = False) -> float:
+    """Microseconds a call of ``run`` takes on the device.  ``graph``: the calls are captured into one CUDA
+    graph and replayed, as the engine replays the kernels of a step of single tokens, so that the host's
+    time to launch does not count."""
     import torch
     for _ in range(3):
         run()
     torch.cuda.synchronize()
+    if graph:
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(iters):
+                run()
+        g.replay()
+        torch.cuda.synchronize()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        g.replay()
+        end.record()
+        torch.cuda.synchronize()
+        return begin.elapsed_time(end) * 1e3 / iters
     begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     begin.record()
     for _ in range(iters):
@@ -949,11 +965,199 @@ def ketalix_kernels(s: dict, tokens: int, batch: int, ctx: int, peaks: dict) -> 
     return rows
 
 
+# ------------------------------------------------------------------------------------------------
+# --design logivik: the Logivik design beside a Ketalix model of equal layer sizes (the engine's
+# other design with paged attention layers and recurrent layers in turn)
+
+def logivik_config(s: dict) -> dict:
+    """Windowed latent attention, delta rule, latent attention with a rotated part, delta rule, and again;
+    every layer with a feed-forward.  Latents of 512 (+ 64 rotated), heads of 128; the delta layers have
+    width / 256 heads with keys of 128 and values of 256 (the state of Ketalix's recurrent layers)."""
+    d, h, w = s["dim"], s["heads"], s["width"]
+    win = {"heads": h, "dim": d, "vdim": d, "kv_rank": 512, "q_rank": 3 * w // 4, "scale": d ** -0.5,
+           "mask": {"size": s["window"]}}
+    rot = {"heads": h, "dim": d, "rot_dim": 64, "vdim": d, "kv_rank": 512, "scale": (d + 64) ** -0.5,
+           "rot": {"base": 1e6, "dims": 64, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    delta = {"heads": w // 256, "kv_heads": max(1, w // 512), "dim": 128, "vdim": 256, "conv": 4}
+    mlp = {"kind": "dense", "ff": s["ff"]}
+    order = [("latent_attention_2", win), ("delta", delta), ("latent_attention", rot), ("delta", delta)]
+    layers = [{"type": order[i % 4][0], "mixer": order[i % 4][1], "mlp": mlp} for i in range(s["layers"])]
+    return {"architecture": "Logivik", "vocab": s["vocab"], "width": w, "norm": {"eps": 1e-6},
+            "embedding": {"scale": 1.0}, "layers": layers}
+
+
+def logivik_kernels(s: dict, tokens: int, batch: int, ctx: int, peaks: dict) -> list[dict]:
+    """Every kernel of the design alone, beside the like kernel of the Ketalix path at the same shape:
+    time, achieved bytes or flops per second, and the fraction of the measured peak."""
+    import torch
+    from types import SimpleNamespace
+    from tokamak_b200.csrc import ops
+    dev = "cuda"
+    gen = torch.Generator(device=dev).manual_seed(0)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+    err = torch.zeros(4, dtype=torch.int32, device=dev)
+    hq, hkv, d, page, win, width = s["heads"], s["kv_heads"], s["dim"], 16, s["window"], s["width"]
+    rank, rot = 512, 64
+    bf = lambda *shape: torch.randn(shape, device=dev, generator=gen).bfloat16()
+    rows = []
+
+    def row(kernel, like, us, us_like, nbytes=0, flops=0.0, like_bytes=0, like_flops=0.0, note=""):
+        r = {"kernel": kernel, "like": like, "us": round(us, 1), "like_us": round(us_like, 1) if us_like else None}
+        for name, t, fl, nb in (("", us, flops, nbytes), ("like_", us_like, like_flops or flops, like_bytes or nbytes)):
+            if not t:
+                continue
+            if fl:
+                r[name + "bf16_frac"] = round(fl / (t * 1e-6) / 1e12 / peaks["bf16_tflops"], 4)
+            elif nb:
+                r[name + "hbm_frac"] = round(nb / (t * 1e-6) / 1e9 / peaks["hbm_gbs"], 4)
+        if note:
+            r["note"] = note
+        rows.append(r)
+
+    sinks = torch.randn(hq, device=dev, generator=gen)
+    # ---- attention over a prompt of `tokens` tokens
+    pages_pf = -(-tokens // page)
+    table = torch.randperm(pages_pf, device=dev, generator=gen).to(torch.int32).view(1, pages_pf)
+    positions, zeros = torch.arange(tokens, dtype=torch.int32, device=dev), torch.zeros(tokens, dtype=torch.int32, device=dev)
+    step_pf = SimpleNamespace(positions=positions, tok_req=zeros, req_q_start=i32([0]), req_q_len=i32([tokens]),
+                              req_kv_len=i32([tokens]), req_slot=i32([0]), err=err)
+    tiles = i32([x for t in reversed(range(-(-tokens // 64))) for x in (0, t)])
+    kc, vc = bf(pages_pf, hkv, page, d), bf(pages_pf, hkv, page, d)
+    q = bf(tokens, hq, d)
+    out = torch.empty_like(q)
+    rec, n_parts, n_split = ops.prefill_tc_records([0], [tokens], [tokens], [0], heads=hq, sms=ops.sm_count(q.device))
+    items = ops.PrefillItems(torch.from_numpy(rec).to(dev), n_parts, n_split)
+    like_pf = lambda w: _time_us(lambda: ops.attention_prefill_tc(q, out, kc, vc, items, table, err, scale=d ** -0.5,
+                                                                  window=w, softcap=30.0, sinks=sinks))
+    for name, dr, w, sk in (("latent attention, prompt (rotated part, sink)", rot, None, sinks),
+                            ("latent attention, prompt (window)", 0, win, None)):
+        cache = bf(pages_pf, 1, page, rank + dr) * 0.3
+        ql = torch.randn(tokens, hq, rank + dr, device=dev, generator=gen) * 0.1
+        ol = torch.empty(tokens, hq, rank, dtype=torch.bfloat16, device=dev)
+        keys = sum(min(i + 1, w or tokens) for i in range(tokens))
+        us = _time_us(lambda: ops.attention_latent(ql, ol, cache, rank, step_pf, table, scale=0.07, window=w, sinks=sk,
+                                                   tiles=tiles), iters=5)
+        row(name, "attention, prompt (cap + sink), same window", us, like_pf(w),
+            flops=2.0 * keys * hq * (2 * rank + dr), like_flops=4.0 * keys * hq * d,
+            note="scores and sums in the latent space: 2 x 512 (+ 64) multiply-adds a key and head against 2 x 128, "
+                 "on mma.sync with both column halves forming the scores")
+    # ---- attention of `batch` single tokens at context `ctx`
+    pages_req = -(-ctx // page)
+    table_d = torch.randperm(batch * pages_req, device=dev, generator=gen).to(torch.int32).view(batch, pages_req)
+    it, pos = i32(list(range(batch))), i32([ctx - 1] * batch)
+    step_d = SimpleNamespace(positions=pos, tok_req=it, req_q_start=it, req_q_len=i32([1] * batch),
+                             req_kv_len=i32([ctx] * batch), req_slot=it, err=err)
+    kc, vc = bf(batch * pages_req, hkv, page, d), bf(batch * pages_req, hkv, page, d)
+    qd = bf(batch, hq, d)
+    outd = torch.empty_like(qd)
+
+    def like_dec(w):
+        n_splits = ops.decode_splits(batch, hkv, min(ctx, w or ctx))
+        scratch = torch.empty(batch * hq * n_splits * (d + 2), dtype=torch.float32, device=dev)
+        return _time_us(lambda: ops.attention_decode(qd, outd, kc, vc, it, pos, it, it, table_d, err, scale=d ** -0.5,
+                                                     window=w, n_splits=n_splits, scratch=scratch, softcap=30.0, sinks=sinks),
+                        graph=True)
+    for name, dr, w, sk in (("latent attention, single tokens (rotated part, sink)", rot, None, sinks),
+                            ("latent attention, single tokens (window)", 0, win, None)):
+        cache = bf(batch * pages_req, 1, page, rank + dr) * 0.3
+        ql = torch.randn(batch, hq, rank + dr, device=dev, generator=gen) * 0.1
+        ol = torch.empty(batch, hq, rank, dtype=torch.bfloat16, device=dev)
+        n_splits = ops.latent_decode_splits(ql.device, batch, ctx, w)
+        us = _time_us(lambda: ops.attention_latent(ql, ol, cache, rank, step_d, table_d, scale=0.07, window=w, sinks=sk,
+                                                   items=it, n_splits=n_splits), graph=True)
+        seen = min(ctx, w or ctx)
+        row(name, "attention, single tokens (cap + sink), same window", us, like_dec(w),
+            nbytes=batch * seen * (rank + dr) * 2, like_bytes=batch * 2 * hkv * seen * d * 2)
+    # ---- what stands between the input projection and attention
+    cols = hq * (d + rot) + rank + rot + hq * d
+    proj = bf(tokens, cols)
+    cache = torch.zeros(pages_pf, 1, page, rank + rot, dtype=torch.bfloat16, device=dev)
+    table_w = torch.arange(pages_pf, dtype=torch.int32, device=dev).view(1, pages_pf)
+    freq = (1.0 / (1e6 ** (torch.arange(0, rot, 2, dtype=torch.float32) / rot))).to(dev)
+    rope = ops.rope_table(positions, freq, 1.1)
+    q_abs = torch.randn(hq, tokens, rank, device=dev, generator=gen)
+    ones_r = torch.ones(rank, device=dev)
+    prep = lambda: ops.latent_prepare(proj, cache, positions, zeros, i32([0]), table_w, err, kv_off=hq * (d + rot), rank=rank,
+                                      rot=rot, kv_norm_w=ones_r, eps=1e-6, table=rope, q_abs=q_abs, q_off=0,
+                                      q_head_cols=d + rot, q_rot_off=d)
+    qkv = bf(tokens, (hq + 2 * hkv) * d)
+    kc2, vc2 = (torch.zeros((pages_pf, hkv, page, d), dtype=torch.bfloat16, device=dev) for _ in range(2))
+    qo = torch.empty(tokens, hq, d, dtype=torch.bfloat16, device=dev)
+    rope_d = ops.rope_table(positions, (1.0 / (1e6 ** (torch.arange(0, d, 2, dtype=torch.float32) / d))).to(dev))
+    len_n = i32([tokens])
+    pairs = lambda: ops.qkv_pairs(qkv, qo, kc2, vc2, positions, zeros, i32([0]), table_w, rope_d, err, n_q_heads=hq,
+                                  n_kv_heads=hkv, rotary_dim=d, unit_norm_eps=1e-6, req_q_len=len_n, req_kv_len=len_n)
+    row("latent norm + rotated parts + cache write + query rows (float32)", "pair rotation + unit norm + page write",
+        _time_us(prep), _time_us(pairs),
+        nbytes=tokens * ((rank + rot + hq * rot) * 2 + (rank + rot) * 2 + hq * rank * 4 + hq * (rank + rot) * 4),
+        like_bytes=qkv.numel() * 2 + qo.numel() * 2 + 2 * tokens * hkv * d * 2)
+    o_h = bf(hq, tokens, d)
+    row("heads back to token rows + sigmoid gate", None, _time_us(lambda: ops.heads_gate(o_h, proj, cols - hq * d)), 0.0,
+        nbytes=3 * tokens * hq * d * 2)
+    # ---- the norm behind a sublayer
+    resid, branch = torch.randn(tokens, width, device=dev, generator=gen), bf(tokens, width)
+    w1, w2, w3 = (torch.ones(width, device=dev) for _ in range(3))
+    normed = torch.empty(tokens, width, dtype=torch.bfloat16, device=dev)
+    row("output norm + residual, the stream handed on unnormalised", "output norm + layer scale + residual + input norm",
+        _time_us(lambda: ops.branch_norm_add(resid, branch, w1, None, 1e-6, None, normed, 0.0)),
+        _time_us(lambda: ops.branch_norm_add(resid, branch, w1, w2, 1e-6, w3, normed, 1e-6)), nbytes=tokens * width * (2 + 8 + 2))
+    # ---- the recurrences
+    gh, gkh, gk, gv, taps, rk = width // 256, max(1, width // 512), 128, 256, 4, 16
+    rowlen = 2 * gkh * gk + 2 * gh * gv + 2 * gh
+    rowlen_g = 2 * gh * gk + 2 * gh * gv + rk
+    for name, n, n_req in (("prompt", tokens, 1), ("single tokens", batch, batch)):
+        projd, projg = bf(n, rowlen) * 0.5, bf(n, rowlen_g) * 0.5
+        conv = torch.randn(2 * gkh * gk + gh * gv, taps, device=dev, generator=gen) * 0.5
+        a_log, dt_b = torch.randn(gh, device=dev, generator=gen) * 0.5, torch.randn(gh, device=dev, generator=gen) * 0.5
+        floats, _ = ops.delta_record_floats(gh, gkh, gk, gv, taps)
+        records = torch.zeros(n_req, floats, device=dev)
+        per = n // n_req
+        starts, lens, slots = i32([i * per for i in range(n_req)]), i32([per] * n_req), i32(list(range(n_req)))
+        tok_req = torch.arange(n, dtype=torch.int32, device=dev) // per
+        offs = dict(q_off=0, k_off=gkh * gk, v_off=2 * gkh * gk, b_off=2 * gkh * gk + 2 * gh * gv, a_off=2 * gkh * gk + 2 * gh * gv + gh)
+        dprep = lambda: ops.delta_prepare(projd, conv, a_log, dt_b, records, tok_req, starts, lens, slots, err,
+                                          dtype=torch.bfloat16, heads=gh, kv_heads=gkh, key_dim=gk, value_dim=gv,
+                                          unit_eps=1e-6, q_scale=gk ** -0.5, **offs)
+        qf, kf, vf, bt, gg = dprep()
+        dscan = lambda: ops.delta_scan(qf, kf, vf, bt, gg, records, starts, lens, slots, err)
+        w2a, bias = bf(gh * gk, rk) * 0.1, torch.randn(gh * gk, device=dev, generator=gen)
+        state = torch.zeros(n_req, gh, gk, gv, device=dev)
+        gprep = lambda: ops.gla_prepare(projg, 0, gh * gk, 2 * gh * gk, 2 * gh * gk + 2 * gh * gv, w2a, bias, heads=gh,
+                                        key_dim=gk, value_dim=gv, tau=16.0, q_scale=gk ** -0.5)
+        gp = gprep()
+        gscan = lambda: ops.gla_scan(gp, state, starts, lens, slots, err)
+        single = n_req > 1          # kernels of a step of single tokens are timed as the engine runs them: from a graph
+        us, us_like = _time_us(dscan, graph=single), _time_us(gscan, graph=single)
+        state_bytes = 2 * n_req * gh * gk * gv * 4
+        r = {"kernel": f"delta rule recurrence, {name}", "like": f"gla recurrence, {name}", "us": round(us, 1),
+             "like_us": round(us_like, 1),
+             "hbm_frac": round((state_bytes + n * (2 * gkh * gk + 2 * gh * gv + 2 * gh) * 4) / (us * 1e-6) / 1e9 / peaks["hbm_gbs"], 4),
+             "like_hbm_frac": round((state_bytes + gp.numel() * 4 + n * gh * gv * 4) / (us_like * 1e-6) / 1e9 / peaks["hbm_gbs"], 4),
+             "fp32_tflops": round(8.0 * n * gh * gk * gv / (us * 1e-6) / 1e12, 2),
+             "like_fp32_tflops": round(4.0 * n * gh * gk * gv / (us_like * 1e-6) / 1e12, 2),
+             "note": "float32 on the CUDA cores, token by token; the delta rule reads the state twice a token "
+                     "(S^T k before the write, S^T q after it): 8 flops a state element against 4"}
+        rows.append(r)
+        row(f"delta rule float32 inputs (convolution, silu, unit norm, beta, decay), {name}",
+            f"gla float32 inputs (scaled q, k, decays, v), {name}", _time_us(dprep, graph=single),
+            _time_us(gprep, graph=single),
+            nbytes=n * (2 * gkh * gk + gh * gv + 2 * gh) * (2 + 4), like_bytes=n * (2 * gh * gk + gh * gv + rk) * 2 + gp.numel() * 4)
+    assert err.tolist()[0] == 0
+    return rows
+
+
+DESIGNS = {
+    "ketalix": dict(name="Ketalix", config=ketalix_config, twin=("qwen3_twin", qwen3_twin), kernels=ketalix_kernels),
+    "logivik": dict(name="Logivik", config=logivik_config, twin=("ketalix_twin", ketalix_config), kernels=logivik_kernels),
+}
+
+
 def design_compare(args) -> int:
-    """Prefill and decode throughput of the Ketalix design beside a Qwen3 model of equal layer sizes
-    (random weights), and the design's kernels alone beside their like kernels."""
+    """Prefill and decode throughput of a design beside the engine's closest other model of equal layer
+    sizes (random weights), and the design's kernels alone beside their like kernels."""
     import torch
     from tokamak_b200.engine.core import random_core
+    design = DESIGNS[args.design]
     s = KETALIX_SIZES[args.design_sizes]
     peaks = load_peaks()
     ctx, pf_tokens, batch = args.seq_len, args.prefill_tokens, args.batch
@@ -962,7 +1166,8 @@ def design_compare(args) -> int:
     sampler = ClockSampler(torch.cuda.current_device())
     sampler.start()
     models = {}
-    for name, raw, vocab in (("ketalix", ketalix_config(s), s["vocab"]), ("qwen3_twin", qwen3_twin(s), s["vocab"])):
+    twin_name, twin_config = design["twin"]
+    for name, raw, vocab in ((args.design, design["config"](s), s["vocab"]), (twin_name, twin_config(s), s["vocab"])):
         core = random_core(raw, seed=0, std=0.02, dtype="bfloat16", max_seq_len=max(ctx, pf_tokens), page_size=16,
                            pool_tokens=max(batch * ctx, pf_tokens + 64), max_slots=batch,
                            max_step_tokens=max(pf_tokens, batch * ctx))
@@ -979,9 +1184,9 @@ def design_compare(args) -> int:
                                      / peaks["hbm_gbs"], 4)}
         del core
         torch.cuda.empty_cache()
-    kernels = ketalix_kernels(s, pf_tokens, batch, ctx, peaks)
+    kernels = design["kernels"](s, pf_tokens, batch, ctx, peaks)
     clocks = sampler.stop()
-    print(json.dumps({"design": "Ketalix", "sizes": {**s, "name": args.design_sizes}, "batch": batch, "seq_len": ctx,
+    print(json.dumps({"design": design["name"], "sizes": {**s, "name": args.design_sizes}, "batch": batch, "seq_len": ctx,
                       "prefill_tokens": pf_tokens, "steps": args.steps, "warmup": args.warmup, "dtype": "bf16",
                       "data": "synthetic: seeded random weights, uniform random token ids", "models": models,
                       "kernels": kernels, "peaks": peaks, "clocks": clocks}))
@@ -1051,9 +1256,10 @@ def main() -> int:
     ap.add_argument("--sizes", default="8b", choices=["0.6b", "8b", "14b", "32b"],
                     help="layer sizes: of --workload (0.6b, 8b), or of the decode/prefill run (8b, the metric's "
                          "own, 14b, 32b)")
-    ap.add_argument("--design", default=None, choices=["ketalix"],
-                    help="measure another design instead: its prefill and decode throughput beside a Qwen3 model of "
-                         "equal layer sizes, and its kernels alone beside their like kernels (--design-sizes)")
+    ap.add_argument("--design", default=None, choices=["ketalix", "logivik"],
+                    help="measure another design instead: its prefill and decode throughput beside the engine's closest "
+                         "other model of equal layer sizes (Ketalix beside Qwen3, Logivik beside Ketalix), and its kernels "
+                         "alone beside their like kernels (--design-sizes)")
     ap.add_argument("--design-sizes", default="2b", choices=sorted(KETALIX_SIZES))
     ap.add_argument("--num-requests", type=int, default=32)
     ap.add_argument("--max-new-cap", type=int, default=256)

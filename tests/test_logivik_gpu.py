@@ -506,7 +506,7 @@ def test_delta_rule_is_bit_equal_however_the_tokens_are_cut_and_split():
     o2, s2 = run([2, 7, 1, 1, 16, 8, 9, 23])
     assert torch.equal(o1, o2) and torch.equal(s1, s2)
     assert not s1[0].any() and not s1[1, H * dk * dv:].any()
-    for cols in (8, 16, 32):             # other splits of the columns add in another order: equal to rounding
+    for cols in (16, 32, 64):            # other splits of the columns add in another order: equal to rounding
         o3, s3 = run([T], cols)
         o4, s4 = run([5, 62], cols)
         assert torch.equal(o3, o4) and torch.equal(s3, s4)

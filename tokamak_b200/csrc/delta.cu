@@ -163,47 +163,54 @@ __device__ __forceinline__ void cp_async4(float* dst, const float* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(d), "l"(src) : "memory");
 }
 
-// One block per (request, head, kCols value channels).  A thread owns kRows rows of one column of the
-// state in registers: lane -> (column = lane % kCols, row group within the warp = lane / kCols), the
-// warps hold further row groups.  Per token every thread forms its share of S^T k and S^T q from the
-// decayed state, the shares meet over shuffles and shared memory (added in a fixed order), and since
+// One block per (request, head, kDeltaWarps * 2 kCP value channels); every warp owns kCP pairs of
+// neighbouring columns of the state for itself: lane -> (pair = lane % kCP, row group = lane / kCP), a
+// thread keeps kRows rows of its two columns in registers as float2, so that every multiply-add is one
+// packed instruction on both columns and a row's k and q are loaded once for the two.  Per token every
+// thread forms its share of S^T k and S^T q from the decayed state, the shares of a column meet over
+// shuffles inside the warp (a fixed order), and since
 //   o = (g S + k u^T)^T q = (g S)^T q + u (k . q)
-// one meeting per token is enough.  Tokens are staged in batches of kDeltaBatch through shared
-// memory, the next batch on its way (cp.async) while this one is worked through.
-template <int kCols, int kRows>
+// one meeting per token is enough.  No barrier stands between two tokens: the warps of a block only
+// share the staging of the inputs, which come in batches of kDeltaBatch tokens through shared memory,
+// the next batch on its way (cp.async) while this one is worked through.
+template <int kCP, int kRows>
 __global__ void __launch_bounds__(kDeltaWarps * 32) delta_scan_kernel(DeltaScanParams p) {
-  constexpr int kSub = 32 / kCols;                     // row groups inside a warp
-  constexpr int kGroups = kDeltaWarps * kSub;
-  constexpr int kRowsAll = kGroups * kRows;            // rows the block can hold (>= dk)
+  constexpr int kGroups = 32 / kCP;                    // row groups of a warp
+  constexpr int kRowsAll = kGroups * kRows;            // rows a warp can hold (>= dk)
+  constexpr int kCols = kDeltaWarps * 2 * kCP;         // columns of a block
   __shared__ __align__(16) float s_q[2][kDeltaBatch][kRowsAll];
   __shared__ __align__(16) float s_k[2][kDeltaBatch][kRowsAll];
-  __shared__ float s_v[2][kDeltaBatch][kCols];
-  __shared__ float s_beta[2][kDeltaBatch], s_g[2][kDeltaBatch], s_kq[kDeltaBatch];
-  __shared__ float s_red[2][2][kDeltaWarps][kCols];    // [parity][a | b][warp][column]
+  __shared__ __align__(8) float s_v[2][kDeltaBatch][kCols];
+  __shared__ float s_beta[2][kDeltaBatch], s_g[2][kDeltaBatch], s_kq[2][kDeltaBatch];
   pdl_trigger();
   pdl_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int col = lane % kCols, sub = lane / kCols;
-  const int group = warp * kSub + sub;
-  const int row0 = group * kRows;
+  const int pair = lane % kCP, sub = lane / kCP;
+  const int row0 = sub * kRows;
   const int r = blockIdx.z, h = blockIdx.y;
   const int c0 = blockIdx.x * kCols;
+  const int bcol = 2 * (warp * kCP + pair);            // this thread's first column within the block
   const int hk = h / (p.heads / p.kv_heads);
   const int n = p.req_q_len[r], t0 = p.req_q_start[r];
   const int slot = p.req_slot[r];
   if (slot < 0 || slot >= p.n_slots) { if (threadIdx.x == 0) set_error(p.err, kErrRequest, r, slot, p.n_slots); return; }
   const int dk = p.dk, dv = p.dv;
-  const bool col_ok = c0 + col < dv;
-  float* S = p.state + (size_t)slot * p.rec_stride + (size_t)h * dk * dv;
+  const bool ok0 = c0 + bcol < dv, ok1 = c0 + bcol + 1 < dv;
+  float* S = p.state + (size_t)slot * p.rec_stride + (size_t)h * dk * dv + c0 + bcol;
 
-  float st[kRows];
+  float2 st[kRows];
 #pragma unroll
-  for (int i = 0; i < kRows; ++i) st[i] = (col_ok && row0 + i < dk) ? S[(size_t)(row0 + i) * dv + c0 + col] : 0.0f;
-  // rows beyond dk read q = k = 0 from shared memory and stay zero
+  for (int i = 0; i < kRows; ++i) {
+    const bool row_ok = row0 + i < dk;
+    st[i].x = (ok0 && row_ok) ? S[(size_t)(row0 + i) * dv] : 0.0f;
+    st[i].y = (ok1 && row_ok) ? S[(size_t)(row0 + i) * dv + 1] : 0.0f;
+  }
+  // rows beyond dk read q = k = 0 from shared memory and stay zero; so do columns beyond dv (v = 0)
   for (int e = threadIdx.x; e < 2 * kDeltaBatch * kRowsAll; e += blockDim.x) {
     (&s_q[0][0][0])[e] = 0.0f;
     (&s_k[0][0][0])[e] = 0.0f;
   }
+  for (int e = threadIdx.x; e < 2 * kDeltaBatch * kCols; e += blockDim.x) (&s_v[0][0][0])[e] = 0.0f;
   __syncthreads();
 
   auto stage = [&](int b0, int buf) {
@@ -226,54 +233,66 @@ __global__ void __launch_bounds__(kDeltaWarps * 32) delta_scan_kernel(DeltaScanP
   };
 
   if (n > 0) stage(0, 0);
-  int parity = 0;
   for (int b0 = 0, buf = 0; b0 < n; b0 += kDeltaBatch, buf ^= 1) {
     const int cnt = min(kDeltaBatch, n - b0);
-    if (b0 + kDeltaBatch < n) {
-      stage(b0 + kDeltaBatch, buf ^ 1);
-      asm volatile("cp.async.wait_group 1;\n" ::: "memory");
-    } else {
-      asm volatile("cp.async.wait_group 0;\n" ::: "memory");
-    }
-    __syncthreads();
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+    __syncthreads();          // this batch is there, and every warp has left the buffer that is staged next
+    if (b0 + kDeltaBatch < n) stage(b0 + kDeltaBatch, buf ^ 1);
     // k . q of every staged token: one warp a token, lanes over the rows, added in a fixed order
     if (warp < cnt) {
       float d = 0.0f;
       for (int x = lane; x < dk; x += 32) d += s_k[buf][warp][x] * s_q[buf][warp][x];
       d = warp_sum(d);
-      if (lane == 0) s_kq[warp] = d;
+      if (lane == 0) s_kq[buf][warp] = d;
     }
     __syncthreads();
-    for (int i = 0; i < cnt; ++i) {
+    const float* kq_row = &s_k[buf][0][row0];
+    const float* qq_row = &s_q[buf][0][row0];
+    float* out_row = p.out + ((size_t)(t0 + b0) * p.heads + h) * dv + c0 + bcol;
+#pragma unroll 4
+    for (int i = 0; i < cnt; ++i, kq_row += kRowsAll, qq_row += kRowsAll, out_row += (size_t)p.heads * dv) {
       const float gt = s_g[buf][i];
-      float a = 0.0f, b = 0.0f;
+      const float2 g2 = make_float2(gt, gt);
+      float2 kk[kRows];
+      float2 a2 = make_float2(0.0f, 0.0f), b2 = a2, a3 = a2, b3 = a2;
 #pragma unroll
-      for (int x = 0; x < kRows; ++x) {
-        st[x] *= gt;
-        a = fmaf(st[x], s_k[buf][i][row0 + x], a);
-        b = fmaf(st[x], s_q[buf][i][row0 + x], b);
+      for (int x = 0; x < kRows; x += 4) {
+        const float4 k4 = *reinterpret_cast<const float4*>(kq_row + x);
+        const float4 q4 = *reinterpret_cast<const float4*>(qq_row + x);
+        kk[x] = make_float2(k4.x, k4.x); kk[x + 1] = make_float2(k4.y, k4.y);
+        kk[x + 2] = make_float2(k4.z, k4.z); kk[x + 3] = make_float2(k4.w, k4.w);
+        st[x] = mul2(st[x], g2); st[x + 1] = mul2(st[x + 1], g2);
+        st[x + 2] = mul2(st[x + 2], g2); st[x + 3] = mul2(st[x + 3], g2);
+        a2 = fma2(st[x], kk[x], a2); a3 = fma2(st[x + 1], kk[x + 1], a3);
+        a2 = fma2(st[x + 2], kk[x + 2], a2); a3 = fma2(st[x + 3], kk[x + 3], a3);
+        b2 = fma2(st[x], make_float2(q4.x, q4.x), b2); b3 = fma2(st[x + 1], make_float2(q4.y, q4.y), b3);
+        b2 = fma2(st[x + 2], make_float2(q4.z, q4.z), b2); b3 = fma2(st[x + 3], make_float2(q4.w, q4.w), b3);
       }
+      a2 = add2(a2, a3); b2 = add2(b2, b3);
 #pragma unroll
-      for (int off = kCols; off < 32; off <<= 1) {
-        a += __shfl_xor_sync(0xffffffffu, a, off);
-        b += __shfl_xor_sync(0xffffffffu, b, off);
+      for (int off = kCP; off < 32; off <<= 1) {
+        const float2 ao = make_float2(__shfl_xor_sync(0xffffffffu, a2.x, off), __shfl_xor_sync(0xffffffffu, a2.y, off));
+        const float2 bo = make_float2(__shfl_xor_sync(0xffffffffu, b2.x, off), __shfl_xor_sync(0xffffffffu, b2.y, off));
+        a2 = add2(a2, ao); b2 = add2(b2, bo);
       }
-      if (sub == 0) { s_red[parity][0][warp][col] = a; s_red[parity][1][warp][col] = b; }
-      __syncthreads();
-      float at = 0.0f, bt = 0.0f;
+      const float bt = s_beta[buf][i];
+      const float2 v2 = *reinterpret_cast<const float2*>(&s_v[buf][i][bcol]);
+      const float2 u2 = make_float2(bt * (v2.x - a2.x), bt * (v2.y - a2.y));
 #pragma unroll
-      for (int w = 0; w < kDeltaWarps; ++w) { at += s_red[parity][0][w][col]; bt += s_red[parity][1][w][col]; }
-      const float u = s_beta[buf][i] * (s_v[buf][i][col] - at);
-#pragma unroll
-      for (int x = 0; x < kRows; ++x) st[x] = fmaf(s_k[buf][i][row0 + x], u, st[x]);
-      if (group == 0 && col_ok) p.out[((size_t)(t0 + b0 + i) * p.heads + h) * dv + c0 + col] = bt + u * s_kq[i];
-      parity ^= 1;
+      for (int x = 0; x < kRows; ++x) st[x] = fma2(kk[x], u2, st[x]);
+      if (sub == 0) {
+        const float kq = s_kq[buf][i];
+        if (ok0) out_row[0] = b2.x + u2.x * kq;
+        if (ok1) out_row[1] = b2.y + u2.y * kq;
+      }
     }
-    __syncthreads();      // the buffer is staged again two batches on; s_kq at the next batch
   }
 #pragma unroll
   for (int i = 0; i < kRows; ++i) {
-    if (col_ok && row0 + i < dk) S[(size_t)(row0 + i) * dv + c0 + col] = st[i];
+    if (row0 + i < dk) {
+      if (ok0) S[(size_t)(row0 + i) * dv] = st[i].x;
+      if (ok1) S[(size_t)(row0 + i) * dv + 1] = st[i].y;
+    }
   }
 }
 
@@ -314,14 +333,14 @@ TK_API int tk_delta_prepare(const void* x, const float* parts, int n_parts, long
   return (int)e;
 }
 
-// Columns of the state that one block takes: fewer where the heads alone would leave SMs idle.  It
-// follows from the model's sizes only, never from the batch, so that a position's sums are always
-// added in the same order.
+// Columns of the state that one block takes (8 warps of 1, 2 or 4 pairs of columns each): fewer where
+// the heads alone would leave the SMs' schedulers without a warp, and never so many that a thread would
+// hold more than 32 rows.  It follows from the model's sizes only, never from the batch, so that a
+// position's sums are always added in the same order.
 TK_API int tk_delta_scan_cols(int heads, int dk, int dv) {
-  int cols = 32;
-  while (cols > 8 && (heads * ((dv + cols - 1) / cols) < 96 || cols / 2 >= dv)) cols /= 2;
-  (void)dk;
-  return cols;
+  int cp = 4;
+  while (cp > 1 && ((long long)heads * dv / (2 * cp) < 500 || dk * cp / 32 > 32)) cp /= 2;
+  return 2 * cp * tk::kDeltaWarps;
 }
 
 TK_API int tk_delta_scan(const float* q, const float* k, const float* v, const float* beta, const float* g,
@@ -331,12 +350,13 @@ TK_API int tk_delta_scan(const float* q, const float* k, const float* v, const f
   if (n_reqs <= 0) return 0;
   if (cols <= 0) cols = tk_delta_scan_cols(heads, dk, dv);
   if (heads < 1 || kv_heads < 1 || heads % kv_heads || heads > 65535 || n_reqs > 65535 ||
-      (cols != 32 && cols != 16 && cols != 8)) {
+      (cols != 64 && cols != 32 && cols != 16)) {
     return (int)cudaErrorInvalidValue;
   }
-  const int groups = tk::kDeltaWarps * (32 / cols);
+  if (dk < 1 || dk > 256) return (int)cudaErrorInvalidValue;      // a warp holds 256 key channels at most
+  const int cp = cols / (2 * tk::kDeltaWarps);
+  const int groups = 32 / cp;
   const int rows = (dk + groups - 1) / groups;
-  if (dk < 1 || dk > 256) return (int)cudaErrorInvalidValue;      // a block stages 256 key channels at most
   tk::DeltaScanParams p;
   p.q = q; p.k = k; p.v = v; p.beta = beta; p.g = g; p.state = state; p.rec_stride = rec_stride; p.out = out;
   p.req_q_start = req_q_start; p.req_q_len = req_q_len; p.req_slot = req_slot; p.err = err;
@@ -344,15 +364,15 @@ TK_API int tk_delta_scan(const float* q, const float* k, const float* v, const f
   dim3 grid((dv + cols - 1) / cols, heads, n_reqs);
   dim3 block(tk::kDeltaWarps * 32);
   cudaError_t e = cudaSuccess;
-  // only the shapes whose rows fit 256 key channels a block are built
+  // only the shapes that 256 key channels need are built
 #define TK_DELTA_LAUNCH(C, R) e = tk::launch(tk::delta_scan_kernel<C, R>, grid, block, 0, stream, p)
-  if (cols == 32) {
-    if (rows <= 4) TK_DELTA_LAUNCH(32, 4); else if (rows <= 8) TK_DELTA_LAUNCH(32, 8);
-    else if (rows <= 16) TK_DELTA_LAUNCH(32, 16); else TK_DELTA_LAUNCH(32, 32);
-  } else if (cols == 16) {
-    if (rows <= 4) TK_DELTA_LAUNCH(16, 4); else if (rows <= 8) TK_DELTA_LAUNCH(16, 8); else TK_DELTA_LAUNCH(16, 16);
+  if (cp == 4) {
+    if (rows <= 4) TK_DELTA_LAUNCH(4, 4); else if (rows <= 8) TK_DELTA_LAUNCH(4, 8);
+    else if (rows <= 16) TK_DELTA_LAUNCH(4, 16); else TK_DELTA_LAUNCH(4, 32);
+  } else if (cp == 2) {
+    if (rows <= 4) TK_DELTA_LAUNCH(2, 4); else if (rows <= 8) TK_DELTA_LAUNCH(2, 8); else TK_DELTA_LAUNCH(2, 16);
   } else {
-    if (rows <= 4) TK_DELTA_LAUNCH(8, 4); else TK_DELTA_LAUNCH(8, 8);
+    if (rows <= 4) TK_DELTA_LAUNCH(1, 4); else TK_DELTA_LAUNCH(1, 8);
   }
 #undef TK_DELTA_LAUNCH
   return (int)e;

@@ -390,11 +390,11 @@ def latent_kernel_takes(d: int, dv: int) -> bool:
 
 
 def latent_decode_splits(device: torch.device, n_items: int, max_kv_len: int, window: int | None) -> int:
-    """Shares that the keys of a single token are cut into: enough blocks for two rounds over the SMs,
-    at least four 64-key tiles a share.  It follows from the step's bucket, not from its lengths."""
+    """Shares that the keys of a single token are cut into: enough blocks for one round over the SMs,
+    at least two 64-key tiles a share.  It follows from the step's bucket, not from its lengths."""
     tiles = -(-min(max_kv_len, window or max_kv_len) // 64) + 1
-    want = -(-2 * sm_count(device) // max(1, n_items))
-    return max(1, min(want, tiles // 4))
+    want = sm_count(device) // max(1, n_items)
+    return max(1, min(want, tiles // 2, 128))
 
 
 def attention_latent(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, dv: int, step, block_table: torch.Tensor,
@@ -1116,7 +1116,7 @@ def delta_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: torch.Te
     """The gated delta rule ``S = g S; u = beta (v - S^T k); S += k u^T; o = S^T q`` over every request's
     tokens of the step; the states ``[heads, dk, dv]`` lead the requests' float32 ``records`` and are
     advanced in place.  Returns ``o`` float32 ``[tokens, heads, dv]``.  ``cols`` is the number of value
-    channels a block takes (32, 16 or 8; 0: what the sizes of the heads suggest)."""
+    channels a block takes (64, 32 or 16: eight warps of 8, 4 or 2 columns; 0: what the sizes of the heads suggest)."""
     for name, t in (("q", q), ("k", k), ("v", v), ("beta", beta), ("g", g), ("records", records)):
         _want(t, torch.float32, name)
     n, kv_heads, dk = q.shape
