@@ -430,12 +430,13 @@ def _delta_plain(x, conv, a_log, dt_bias, offs, H, HK, dk, dv):
                                              (2, 2, 64, 64, 2), (1, 1, 256, 33, 4)])
 def test_delta_rule_inputs_recurrence_and_state_over_steps(dtype, H, HK, dk, dv, taps):
     """Three requests in slots 2, 0, 3 of 4, fed in two steps of unequal portions (the second step's first
-    tokens read the convolution's tail of the first): inputs, outputs, state and tail against the plain
-    functions run over each request's whole sequence."""
+    tokens read the convolution's tail of the first) and a step of one token each (the kernel of the inputs
+    moves the tails on itself): inputs, outputs, state and tail against the plain functions run over each
+    request's whole sequence."""
     from tokamak_b200.csrc import ops
-    first, second = [9, 1, 30], [2, 5, 1]
+    first, second, third = [9, 1, 30], [2, 5, 1], [1, 1, 1]
     slots = [2, 0, 3]
-    totals = [a + b for a, b in zip(first, second)]
+    totals = [a + b + c for a, b, c in zip(first, second, third)]
     g, proj, conv, a_log, dt_bias, offs = _delta_inputs(dtype, H, HK, dk, dv, taps, totals, seed=dk + dv)
     floats, tail_off = ops.delta_record_floats(H, HK, dk, dv, taps)
     records = torch.zeros(4, floats, device="cuda")
@@ -445,7 +446,7 @@ def test_delta_rule_inputs_recurrence_and_state_over_steps(dtype, H, HK, dk, dv,
     err = new_err()
     got_o = [[] for _ in seqs]
     got_in = [[] for _ in seqs]
-    for lens, at in ((first, [0, 0, 0]), (second, first)):
+    for lens, at in ((first, [0, 0, 0]), (second, first), (third, [a + b for a, b in zip(first, second)])):
         step_proj = torch.cat([seq[a:a + n] for seq, a, n in zip(seqs, at, lens)])
         starts = [0, lens[0], lens[0] + lens[1]]
         tok_req = sum(([r] * n for r, n in enumerate(lens)), [])

@@ -31,7 +31,7 @@ struct DeltaPrepareParams {
   const float* taps;          // [channels, n_taps]: q channels, k channels, v channels
   const float* a_log;         // [heads]
   const float* dt_bias;       // [heads]
-  const float* state;         // the pool of records
+  float* state;               // the pool of records
   long long rec_stride;       // floats per record
   long long tail_off;         // where the tail starts inside a record
   const int* tok_req;
@@ -44,6 +44,7 @@ struct DeltaPrepareParams {
   float* g_out;               // [n_tokens, heads]
   int* err;
   int n_tokens, n_reqs, n_slots, heads, kv_heads, dk, dv, n_taps;
+  int move_tail;              // every request brings one token: the warp that reads a channel's tail also moves it on
   float unit_eps, q_scale;
 };
 
@@ -71,7 +72,7 @@ __global__ void delta_prepare_kernel(DeltaPrepareParams p) {
   const int slot = p.req_slot[r];
   if (slot < 0 || slot >= p.n_slots) { if (lane == 0) set_error(p.err, kErrRequest, t, slot, p.n_slots); return; }
   const int i = t - p.req_q_start[r];          // place of the token among its request's tokens of this step
-  const float* tail = p.state + (size_t)slot * p.rec_stride + p.tail_off;
+  float* tail = p.state + (size_t)slot * p.rec_stride + p.tail_off;
   const int K = p.n_taps;
 
   float* dst = kind == 0 ? p.q_out + ((size_t)t * p.kv_heads + head) * p.dk
@@ -86,6 +87,12 @@ __global__ void delta_prepare_kernel(DeltaPrepareParams p) {
       const float x = s >= 0 ? stacked_ld<T>(p.in, (size_t)(t - i + s) * p.in.row_stride + col0 + e)
                              : tail[(size_t)(K - 1 + s) * channels + chan0 + e];
       acc += w[j] * x;
+    }
+    if (p.move_tail) {
+      // the request's only token of this step: nobody else reads this channel's tail, which now ends with the token's input
+      float* tc = tail + chan0 + e;
+      for (int j = 0; j + 2 < K; ++j) tc[(size_t)j * channels] = tc[(size_t)(j + 1) * channels];
+      if (K > 1) tc[(size_t)(K - 2) * channels] = stacked_ld<T>(p.in, (size_t)t * p.in.row_stride + col0 + e);
     }
     const float y = acc / (1.0f + expf(-acc));
     dst[e] = y;
@@ -304,7 +311,10 @@ TK_API int tk_delta_prepare(const void* x, const float* parts, int n_parts, long
                             long long tail_off, const int* tok_req, const int* req_q_start, const int* req_q_len,
                             const int* req_slot, float* q_out, float* k_out, float* v_out, float* beta_out,
                             float* g_out, int* err, int n_tokens, int n_reqs, int n_slots, int heads, int kv_heads,
-                            int dk, int dv, int n_taps, float unit_eps, float q_scale, int dtype, cudaStream_t stream) {
+                            int dk, int dv, int n_taps, float unit_eps, float q_scale, int dtype, int move_tail_in_place,
+                            cudaStream_t stream) {
+  // move_tail_in_place: the caller vouches that every request brings at least one token, so that as many
+  // tokens as requests means one token each; the kernel of the inputs then moves the tails on itself
   if (n_tokens <= 0 || n_reqs <= 0) return 0;
   if ((x == nullptr) == (parts == nullptr) || heads < 1 || kv_heads < 1 || heads % kv_heads || dk < 1 || dv < 1 ||
       n_taps < 1 || n_taps > tk::kDeltaMaxTaps || n_reqs > 65535) {
@@ -318,12 +328,13 @@ TK_API int tk_delta_prepare(const void* x, const float* parts, int n_parts, long
   p.q_out = q_out; p.k_out = k_out; p.v_out = v_out; p.beta_out = beta_out; p.g_out = g_out; p.err = err;
   p.n_tokens = n_tokens; p.n_reqs = n_reqs; p.n_slots = n_slots; p.heads = heads; p.kv_heads = kv_heads;
   p.dk = dk; p.dv = dv; p.n_taps = n_taps; p.unit_eps = unit_eps; p.q_scale = q_scale;
+  p.move_tail = (n_tokens == n_reqs && move_tail_in_place) ? 1 : 0;
   const int units = 2 * kv_heads + heads;
   dim3 grid(n_tokens, (units + tk::kDeltaPrepWarps - 1) / tk::kDeltaPrepWarps);
   cudaError_t e = cudaSuccess;
   TK_DISPATCH_DTYPE(dtype, T,
                     e = tk::launch(tk::delta_prepare_kernel<T>, grid, dim3(tk::kDeltaPrepWarps * 32), 0, stream, p));
-  if (e != cudaSuccess || n_taps == 1) return (int)e;
+  if (e != cudaSuccess || n_taps == 1 || p.move_tail) return (int)e;
   const int hk = kv_heads * dk, hv = heads * dv;
   dim3 tgrid((2 * hk + hv + 127) / 128, n_reqs);
   TK_DISPATCH_DTYPE(dtype, T,

@@ -1075,7 +1075,8 @@ def delta_prepare(proj: torch.Tensor, taps: torch.Tensor, a_log: torch.Tensor, d
     ``[channels, K]``, channels in the order q, k, v) and silu on q, k and v, q and k heads scaled to
     unit length (q also by ``q_scale``), ``beta = sigmoid(b)`` and ``g = exp(-exp(a_log) softplus(a +
     dt_bias))`` per head.  The convolution reads the inputs before the step from the tail of the
-    requests' ``records`` (float32 ``[slots, floats]``, see :func:`delta_record_floats`) and moves the tail on.
+    requests' ``records`` (float32 ``[slots, floats]``, see :func:`delta_record_floats`) and moves the tail on
+    (every request must bring at least one token: with as many tokens as requests the same kernel does both).
     Returns ``(q [N, Hk, dk], k [N, Hk, dk], v [N, H, dv], beta [N, H], g [N, H])``."""
     _want(taps, torch.float32, "taps"); _want(a_log, torch.float32, "a_log"); _want(dt_bias, torch.float32, "dt_bias")
     _want(records, torch.float32, "records")
@@ -1104,9 +1105,9 @@ def delta_prepare(proj: torch.Tensor, taps: torch.Tensor, a_log: torch.Tensor, d
                                       req_slot.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), beta.data_ptr(),
                                       g.data_ptr(), err.data_ptr(), n, req_slot.numel(), records.shape[0], heads,
                                       kv_heads, key_dim, value_dim, k_taps, float(unit_eps), float(q_scale),
-                                      dtype_code(dtype), _stream()), "delta_prepare")
+                                      dtype_code(dtype), 1, _stream()), "delta_prepare")
     global LAUNCHES
-    LAUNCHES += 1 if k_taps > 1 else 0       # the kernel that moves the tail on
+    LAUNCHES += 1 if k_taps > 1 and n != req_slot.numel() else 0       # the kernel that moves the tail on
     return q, k, v, beta, g
 
 
