@@ -451,10 +451,14 @@ def test_delta_rule_inputs_recurrence_and_state_over_steps(dtype, H, HK, dk, dv,
         starts = [0, lens[0], lens[0] + lens[1]]
         tok_req = sum(([r] * n for r, n in enumerate(lens)), [])
         meta = (dev(torch.tensor(tok_req, dtype=torch.int32)), i32(*starts), i32(*lens), i32(*slots), err)
-        q, k, v, beta, gg = ops.delta_prepare(dev(step_proj), dev(conv), dev(a_log), dev(dt_bias), records, *meta,
-                                              dtype=TORCH[dtype], heads=H, kv_heads=HK, key_dim=dk, value_dim=dv,
-                                              unit_eps=1e-6, q_scale=dk ** -0.5, **offs)
-        # split sums of a product give the same inputs (the tail has moved on: compare on a copy made before)
+        kw = dict(dtype=TORCH[dtype], heads=H, kv_heads=HK, key_dim=dk, value_dim=dv, unit_eps=1e-6, q_scale=dk ** -0.5, **offs)
+        # both launch shapes and the split sums of a product give the same bits (on copies: the tail moves on)
+        halves = dev(torch.stack([step_proj.float() * 0.5, step_proj.float() * 0.5]))
+        others = [ops.delta_prepare(x, dev(conv), dev(a_log), dev(dt_bias), records.clone(), *meta, shape=shape, **kw)
+                  for x, shape in ((dev(step_proj), 1), (dev(step_proj), 2), (halves, 0))]
+        q, k, v, beta, gg = ops.delta_prepare(dev(step_proj), dev(conv), dev(a_log), dev(dt_bias), records, *meta, **kw)
+        for other in others:
+            assert all(torch.equal(a, b) for a, b in zip(other, (q, k, v, beta, gg)))
         o = ops.delta_scan(q, k, v, beta, gg, records, *meta[1:])
         for r, (s, n) in enumerate(zip(starts, lens)):
             got_o[r].append(o[s:s + n].cpu())

@@ -44,20 +44,29 @@ struct DeltaPrepareParams {
   float* g_out;               // [n_tokens, heads]
   int* err;
   int n_tokens, n_reqs, n_slots, heads, kv_heads, dk, dv, n_taps;
-  int move_tail;              // every request brings one token: the warp that reads a channel's tail also moves it on
+  int move_tail;              // every request brings one token: the thread that reads a channel's tail also moves it on
+  int per_warp;               // a warp a unit (many tokens) or a block a unit (few)
   float unit_eps, q_scale;
 };
 
-// One warp per (token, head unit); the units of a token are its q heads, its k heads, its v heads.
+// One head unit of one token at a time; the units of a token are its q heads, its k heads, its v heads.
+// Two shapes of the same arithmetic: with many tokens a warp takes a unit (lanes over the channels, 32 at a
+// time), with few a whole block does (a thread a channel, so that the channels' loads of taps, inputs and
+// tail wait for memory side by side instead of in turn).  The sum of squares of a q or k head is formed the
+// same way in both: every aligned group of 32 channels by a warp's butterfly, the groups added in ascending
+// order; a position's inputs are therefore the same bits whichever shape a step takes.
 template <typename T>
 __global__ void delta_prepare_kernel(DeltaPrepareParams p) {
+  __shared__ float s_group[8];        // key_dim <= 256: at most 8 groups
   pdl_trigger();
   pdl_wait();
-  const int lane = threadIdx.x & 31;
+  const bool per_warp = p.per_warp != 0;
+  const int lane = per_warp ? (threadIdx.x & 31) : threadIdx.x;         // place among the unit's threads
+  const int stride = per_warp ? 32 : blockDim.x;
   const int t = blockIdx.x;
-  const int unit = blockIdx.y * kDeltaPrepWarps + (threadIdx.x >> 5);
+  const int unit = per_warp ? blockIdx.y * kDeltaPrepWarps + (threadIdx.x >> 5) : blockIdx.y;
   const int units = 2 * p.kv_heads + p.heads;
-  if (unit >= units) return;
+  if (unit >= units) return;          // whole warps of the last block of the per-warp shape
   int kind, head;      // 0 = q, 1 = k, 2 = v
   if (unit < p.kv_heads) { kind = 0; head = unit; }
   else if (unit < 2 * p.kv_heads) { kind = 1; head = unit - p.kv_heads; }
@@ -78,8 +87,8 @@ __global__ void delta_prepare_kernel(DeltaPrepareParams p) {
   float* dst = kind == 0 ? p.q_out + ((size_t)t * p.kv_heads + head) * p.dk
              : kind == 1 ? p.k_out + ((size_t)t * p.kv_heads + head) * p.dk
                          : p.v_out + ((size_t)t * p.heads + head) * p.dv;
-  float ss = 0.0f;
-  for (int e = lane; e < d; e += 32) {
+  // one channel: convolution over the step's rows and the tail, silu, the value stored; returns it
+  auto channel = [&](int e) -> float {
     const float* w = p.taps + (size_t)(chan0 + e) * K;
     float acc = 0.0f;
     for (int j = 0; j < K; ++j) {
@@ -96,13 +105,38 @@ __global__ void delta_prepare_kernel(DeltaPrepareParams p) {
     }
     const float y = acc / (1.0f + expf(-acc));
     dst[e] = y;
-    ss += y * y;
+    return y;
+  };
+  float ss = 0.0f;
+  if (kind == 2) {
+    for (int e = lane; e < d; e += stride) channel(e);
+  } else if (per_warp) {
+    // a q or k head has at most 8 groups of 32 channels: their sums of squares are formed after the loop, in order
+    float sq[8];
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+      const int e = lane + 32 * it;
+      sq[it] = 0.0f;
+      if (e < d) { const float y = channel(e); sq[it] = y * y; }
+    }
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+      if (32 * it < d) ss += warp_sum(sq[it]);
+    }
+  } else {
+    const int e = lane;                          // key_dim <= the block's threads: one round
+    float y = 0.0f;
+    if (e < d) y = channel(e);
+    const float group = warp_sum(y * y);         // channels 32 g .. 32 g + 31, g = e / 32 (the same in a warp)
+    if ((threadIdx.x & 31) == 0 && e < d) s_group[e >> 5] = group;
   }
   if (kind != 2) {
-    ss = warp_sum(ss);
+    if (!per_warp) {
+      __syncthreads();       // kind and d are the block's: every thread comes here
+      for (int gi = 0; gi < (d + 31) / 32; ++gi) ss += s_group[gi];
+    }
     const float f = rsqrtf(ss + p.unit_eps) * (kind == 0 ? p.q_scale : 1.0f);
-    __syncwarp();
-    for (int e = lane; e < d; e += 32) dst[e] *= f;     // each lane rescales what it wrote itself
+    for (int e = lane; e < d; e += stride) dst[e] *= f;     // each thread rescales what it wrote itself
   } else if (lane == 0) {
     const size_t row = (size_t)t * p.in.row_stride;
     const float b = stacked_ld<T>(p.in, row + p.b_off + head);
@@ -165,6 +199,10 @@ struct DeltaScanParams {
   int n_reqs, n_slots, heads, kv_heads, dk, dv;
 };
 
+__device__ __forceinline__ void cp_async16f(float* dst, const float* src) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(d), "l"(src) : "memory");
+}
 __device__ __forceinline__ void cp_async4(float* dst, const float* src) {
   const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(d), "l"(src) : "memory");
@@ -220,13 +258,25 @@ __global__ void __launch_bounds__(kDeltaWarps * 32) delta_scan_kernel(DeltaScanP
   for (int e = threadIdx.x; e < 2 * kDeltaBatch * kCols; e += blockDim.x) (&s_v[0][0][0])[e] = 0.0f;
   __syncthreads();
 
+  // q and k rows in 16-byte pieces where the rows allow it (key_dim a multiple of 4, the arrays aligned)
+  const bool vec = (dk & 3) == 0 && ((reinterpret_cast<uintptr_t>(p.q) | reinterpret_cast<uintptr_t>(p.k)) & 15) == 0;
   auto stage = [&](int b0, int buf) {
     const int cnt = min(kDeltaBatch, n - b0);
-    for (int e = threadIdx.x; e < cnt * dk; e += blockDim.x) {
-      const int i = e / dk, x = e - i * dk;
-      const size_t src = ((size_t)(t0 + b0 + i) * p.kv_heads + hk) * dk + x;
-      cp_async4(&s_q[buf][i][x], p.q + src);
-      cp_async4(&s_k[buf][i][x], p.k + src);
+    if (vec) {
+      const int quads = dk >> 2;
+      for (int e = threadIdx.x; e < cnt * quads; e += blockDim.x) {
+        const int i = e / quads, x = (e - i * quads) * 4;
+        const size_t src = ((size_t)(t0 + b0 + i) * p.kv_heads + hk) * dk + x;
+        cp_async16f(&s_q[buf][i][x], p.q + src);
+        cp_async16f(&s_k[buf][i][x], p.k + src);
+      }
+    } else {
+      for (int e = threadIdx.x; e < cnt * dk; e += blockDim.x) {
+        const int i = e / dk, x = e - i * dk;
+        const size_t src = ((size_t)(t0 + b0 + i) * p.kv_heads + hk) * dk + x;
+        cp_async4(&s_q[buf][i][x], p.q + src);
+        cp_async4(&s_k[buf][i][x], p.k + src);
+      }
     }
     for (int e = threadIdx.x; e < cnt * kCols; e += blockDim.x) {
       const int i = e / kCols, x = e - i * kCols;
@@ -312,7 +362,7 @@ TK_API int tk_delta_prepare(const void* x, const float* parts, int n_parts, long
                             const int* req_slot, float* q_out, float* k_out, float* v_out, float* beta_out,
                             float* g_out, int* err, int n_tokens, int n_reqs, int n_slots, int heads, int kv_heads,
                             int dk, int dv, int n_taps, float unit_eps, float q_scale, int dtype, int move_tail_in_place,
-                            cudaStream_t stream) {
+                            int shape, cudaStream_t stream) {
   // move_tail_in_place: the caller vouches that every request brings at least one token, so that as many
   // tokens as requests means one token each; the kernel of the inputs then moves the tails on itself
   if (n_tokens <= 0 || n_reqs <= 0) return 0;
@@ -330,10 +380,15 @@ TK_API int tk_delta_prepare(const void* x, const float* parts, int n_parts, long
   p.dk = dk; p.dv = dv; p.n_taps = n_taps; p.unit_eps = unit_eps; p.q_scale = q_scale;
   p.move_tail = (n_tokens == n_reqs && move_tail_in_place) ? 1 : 0;
   const int units = 2 * kv_heads + heads;
-  dim3 grid(n_tokens, (units + tk::kDeltaPrepWarps - 1) / tk::kDeltaPrepWarps);
+  if (units > 65535 || dk > 256) return (int)cudaErrorInvalidValue;
+  const int widest = dk > dv ? dk : dv;
+  // few tokens: a block a unit, so that a step of single tokens is one memory latency long; many: a warp a unit
+  // (shape 1 / 2: the caller's choice, for tests and measurements; both give the same bits)
+  p.per_warp = shape == 1 ? 1 : shape == 2 ? 0 : ((long long)n_tokens * units >= 4096 ? 1 : 0);
+  const int threads = p.per_warp ? tk::kDeltaPrepWarps * 32 : (widest >= 256 ? 256 : (widest + 31) / 32 * 32);
+  dim3 grid(n_tokens, p.per_warp ? (units + tk::kDeltaPrepWarps - 1) / tk::kDeltaPrepWarps : units);
   cudaError_t e = cudaSuccess;
-  TK_DISPATCH_DTYPE(dtype, T,
-                    e = tk::launch(tk::delta_prepare_kernel<T>, grid, dim3(tk::kDeltaPrepWarps * 32), 0, stream, p));
+  TK_DISPATCH_DTYPE(dtype, T, e = tk::launch(tk::delta_prepare_kernel<T>, grid, dim3(threads), 0, stream, p));
   if (e != cudaSuccess || n_taps == 1 || p.move_tail) return (int)e;
   const int hk = kv_heads * dk, hv = heads * dv;
   dim3 tgrid((2 * hk + hv + 127) / 128, n_reqs);

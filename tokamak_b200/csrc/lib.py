@@ -45,7 +45,7 @@ _SIGNATURES: dict[str, list] = {
     "tk_heads_gate": [_P, _P, _P, c_int, c_longlong, c_int, c_int, _P, c_int, c_int, c_int, c_int, _P],
     "tk_delta_prepare": [_P, _P, c_int, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P,
                          c_longlong, c_longlong, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
-                         c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_int, _P],
+                         c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_int, c_int, _P],
     "tk_delta_scan": [_P, _P, _P, _P, _P, _P, c_longlong, _P, _P, _P, _P, _P,
                       c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P],
     "tk_delta_scan_cols": [c_int, c_int, c_int],

@@ -1069,7 +1069,7 @@ def delta_prepare(proj: torch.Tensor, taps: torch.Tensor, a_log: torch.Tensor, d
                   records: torch.Tensor, tok_req: torch.Tensor, req_q_start: torch.Tensor, req_q_len: torch.Tensor,
                   req_slot: torch.Tensor, err: torch.Tensor, *, dtype: torch.dtype, q_off: int, k_off: int, v_off: int,
                   b_off: int, a_off: int, heads: int, kv_heads: int, key_dim: int, value_dim: int, unit_eps: float,
-                  q_scale: float) -> tuple:
+                  q_scale: float, shape: int = 0) -> tuple:
     """The float32 inputs of the delta-rule recurrence from the columns of the stacked projection
     ``proj`` (type ``dtype``, or float32 partial sums): short causal convolution (``taps`` float32
     ``[channels, K]``, channels in the order q, k, v) and silu on q, k and v, q and k heads scaled to
@@ -1077,6 +1077,8 @@ def delta_prepare(proj: torch.Tensor, taps: torch.Tensor, a_log: torch.Tensor, d
     dt_bias))`` per head.  The convolution reads the inputs before the step from the tail of the
     requests' ``records`` (float32 ``[slots, floats]``, see :func:`delta_record_floats`) and moves the tail on
     (every request must bring at least one token: with as many tokens as requests the same kernel does both).
+    ``shape``: 0 lets the launcher choose a warp (many tokens) or a block (few) per head, 1 and 2 force one;
+    the results are the same bits.
     Returns ``(q [N, Hk, dk], k [N, Hk, dk], v [N, H, dv], beta [N, H], g [N, H])``."""
     _want(taps, torch.float32, "taps"); _want(a_log, torch.float32, "a_log"); _want(dt_bias, torch.float32, "dt_bias")
     _want(records, torch.float32, "records")
@@ -1105,7 +1107,7 @@ def delta_prepare(proj: torch.Tensor, taps: torch.Tensor, a_log: torch.Tensor, d
                                       req_slot.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), beta.data_ptr(),
                                       g.data_ptr(), err.data_ptr(), n, req_slot.numel(), records.shape[0], heads,
                                       kv_heads, key_dim, value_dim, k_taps, float(unit_eps), float(q_scale),
-                                      dtype_code(dtype), 1, _stream()), "delta_prepare")
+                                      dtype_code(dtype), 1, int(shape), _stream()), "delta_prepare")
     global LAUNCHES
     LAUNCHES += 1 if k_taps > 1 and n != req_slot.numel() else 0       # the kernel that moves the tail on
     return q, k, v, beta, g
