@@ -60,9 +60,21 @@ LV_C = {
         _layer("delta", _delta(4, 2, 64, 64, 4), 64),
     ],
 }
+# latents in steps of 16 (the tensor-core attention kernels) with head counts that fill no tile evenly, values
+# narrower than one warp's share of columns, a rotated part turned only in its first half
+LV_D = {
+    "architecture": "Logivik", "vocab": 333, "width": 192, "norm": {"eps": 1e-5}, "embedding": {"scale": 2.0},
+    "layers": [
+        _layer("delta", _delta(6, 3, 96, 48, 2), 160),
+        _layer("latent_attention", _latent(5, 24, 16, 40, 48, 0.16, base=2000.0, dims=8, scaling=(3.0, 48, 6.0, 1.5)), None),
+        _layer("latent_attention_2", _window(7, 16, 24, 32, 40, 0.25, 20), 96),
+        _layer("latent_attention", _latent(18, 8, 32, 16, 80, 0.2), 64),
+    ],
+}
 # (configuration, how the random weights are drawn, page size)
 ALL = {
     "LA": (LV_A, {"seed": 21, "std": 0.08, "norm_std": 0.1}, 16),
     "LB": (LV_B, {"seed": 22, "std": 0.1, "norm_std": 0.1}, 8),
     "LC": (LV_C, {"seed": 23, "std": 0.06, "norm_std": 0.1}, 32),
+    "LD": (LV_D, {"seed": 24, "std": 0.07, "norm_std": 0.1}, 16),
 }

@@ -549,7 +549,7 @@ def test_delta_rule_remembers_a_far_write_and_forgets_by_its_decay():
 # ======================================================================= whole models
 
 LENGTHS = {"LA": [5, 17, 33, 70, 130, 96, 41, 128], "LB": [1, 7, 31, 64, 100, 143, 52, 90],
-           "LC": [3, 40, 77, 150, 64, 110, 25, 95]}
+           "LC": [3, 40, 77, 150, 64, 110, 25, 95], "LD": [2, 66, 129, 20, 90, 151, 47, 80]}
 
 
 def requests_for(tag):
@@ -586,25 +586,25 @@ def replay(tag, dtype, builder, max_tokens, poison=False, max_live=4, **kw):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("tag", ["LA", "LB", "LC"])
+@pytest.mark.parametrize("tag", ["LA", "LB", "LC", "LD"])
 def test_whole_prompts(tag, dtype):
     replay(tag, dtype, traces.whole, max_tokens=192)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("tag", ["LA", "LB", "LC"])
+@pytest.mark.parametrize("tag", ["LA", "LB", "LC", "LD"])
 def test_tail_decoded_one_by_one_across_every_window(tag, dtype):
     replay(tag, dtype, traces.tail_one_by_one, max_tokens=192, tail=60)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("tag", ["LA", "LB", "LC"])
+@pytest.mark.parametrize("tag", ["LA", "LB", "LC", "LD"])
 def test_portions_of_changing_size(tag, dtype):
     replay(tag, dtype, traces.portions, max_tokens=192)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("tag", ["LA", "LB", "LC"])
+@pytest.mark.parametrize("tag", ["LA", "LB", "LC", "LD"])
 def test_mixed_batches_with_pages_and_slots_used_again(tag, dtype):
     replay(tag, dtype, traces.mixed, max_tokens=384, poison=True, seed=7)
     assert sum(LENGTHS[tag]) > 384
