@@ -71,10 +71,19 @@ LV_D = {
         _layer("latent_attention", _latent(18, 8, 32, 16, 80, 0.2), 64),
     ],
 }
+# a latent attention layer with sink and gate but no rotated part (and so no positions at all in the model)
+LV_E = {
+    "architecture": "Logivik", "vocab": 120, "width": 64, "norm": {"eps": 1e-6},
+    "layers": [
+        _layer("latent_attention", {"heads": 4, "dim": 16, "rot_dim": 0, "vdim": 16, "kv_rank": 32, "scale": 0.25}, 64),
+        _layer("delta", _delta(2, 2, 32, 32, 4), None),
+    ],
+}
 # (configuration, how the random weights are drawn, page size)
 ALL = {
     "LA": (LV_A, {"seed": 21, "std": 0.08, "norm_std": 0.1}, 16),
     "LB": (LV_B, {"seed": 22, "std": 0.1, "norm_std": 0.1}, 8),
     "LC": (LV_C, {"seed": 23, "std": 0.06, "norm_std": 0.1}, 32),
     "LD": (LV_D, {"seed": 24, "std": 0.07, "norm_std": 0.1}, 16),
+    "LE": (LV_E, {"seed": 25, "std": 0.1, "norm_std": 0.1}, 16),
 }

@@ -126,18 +126,19 @@ def latent_attention(h, w, m, eps, positions):
     """Latent attention with a rotated part: the keys and values of all heads come from one latent
     per token, one rotated key part is shared by the heads; sink in the softmax; sigmoid output gate."""
     T = h.shape[0]
-    H, d, dr, dv, r = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
+    H, d, dr, dv, r = m["heads"], m["dim"], m.get("rot_dim", 0), m["vdim"], m["kv_rank"]
     q = ROUND(h @ w["q"].T).view(T, H, d + dr)
     dkv = ROUND(h @ w["dkv"].T)
     c = ROUND(rms(dkv[:, :r], eps) * w["dkv.norm"])
-    rot = m["rot"]
-    freqs, mag = yarn_frequencies(rot["dims"], rot["base"], rot.get("scaling"))
-    n_rot = rot["dims"]
     k_rot = dkv[:, r:].clone()
-    k_rot[:, :n_rot] = rotate_pairs(k_rot[:, :n_rot], positions, freqs, mag)
-    k_rot = ROUND(k_rot)
     q_rot = q[..., d:].clone()
-    q_rot[..., :n_rot] = rotate_pairs(q_rot[..., :n_rot], positions, freqs, mag)
+    if dr:
+        rot = m["rot"]
+        n_rot = rot.get("dims", dr)
+        freqs, mag = yarn_frequencies(n_rot, rot["base"], rot.get("scaling"))
+        k_rot[:, :n_rot] = rotate_pairs(k_rot[:, :n_rot], positions, freqs, mag)
+        q_rot[..., :n_rot] = rotate_pairs(q_rot[..., :n_rot], positions, freqs, mag)
+    k_rot = ROUND(k_rot)
     k = torch.cat([ROUND(c @ w["uk"].T).view(T, H, d), k_rot[:, None, :].expand(T, H, dr)], -1)
     v = ROUND(c @ w["uv"].T).view(T, H, dv)
     o = softmax_attention(torch.cat([q[..., :d], q_rot], -1), k, v, m["scale"], None, w["sink"])

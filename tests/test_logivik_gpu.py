@@ -549,7 +549,8 @@ def test_delta_rule_remembers_a_far_write_and_forgets_by_its_decay():
 # ======================================================================= whole models
 
 LENGTHS = {"LA": [5, 17, 33, 70, 130, 96, 41, 128], "LB": [1, 7, 31, 64, 100, 143, 52, 90],
-           "LC": [3, 40, 77, 150, 64, 110, 25, 95], "LD": [2, 66, 129, 20, 90, 151, 47, 80]}
+           "LC": [3, 40, 77, 150, 64, 110, 25, 95], "LD": [2, 66, 129, 20, 90, 151, 47, 80],
+           "LE": [4, 70, 33, 100]}
 
 
 def requests_for(tag):
@@ -608,6 +609,12 @@ def test_portions_of_changing_size(tag, dtype):
 def test_mixed_batches_with_pages_and_slots_used_again(tag, dtype):
     replay(tag, dtype, traces.mixed, max_tokens=384, poison=True, seed=7)
     assert sum(LENGTHS[tag]) > 384
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_latent_attention_without_a_rotated_part(dtype):
+    replay("LE", dtype, traces.portions, max_tokens=128)
+    replay("LE", dtype, traces.mixed, max_tokens=192, poison=True, seed=4)
 
 
 @pytest.mark.parametrize("seed", [1, 2])

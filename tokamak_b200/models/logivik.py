@@ -131,8 +131,11 @@ def _parse_layer(i: int, raw: Mapping[str, Any]) -> LogivikLayer:
         mixer = DeltaLayer(heads=heads, kv_heads=kv, dim=dim, vdim=_positive(m.get("vdim", dim), w + "vdim"),
                            conv=num("conv"))
     elif kind == "latent_attention":
-        rot_dim = num("rot_dim")
-        dims, base, yarn = _parse_rot(m, w, rot_dim)
+        rot_dim = m.get("rot_dim", 0) or 0
+        if isinstance(rot_dim, bool) or int(rot_dim) != rot_dim or rot_dim < 0:
+            raise ConfigError(f"{w}rot_dim must be a non-negative integer, got {rot_dim!r}")
+        rot_dim = int(rot_dim)
+        dims, base, yarn = _parse_rot(m, w, rot_dim) if rot_dim else (0, 1.0, None)     # no rotated part: no positions
         dim = num("dim")
         mixer = LatentLayer(heads=num("heads"), dim=dim, rot_dim=rot_dim, vdim=_positive(m.get("vdim", dim), w + "vdim"),
                             kv_rank=num("kv_rank"), q_rank=None, scale=float(_need(m, "scale", w)), window=None,
